@@ -1,0 +1,153 @@
+/*
+ * sdv2.h - C ABI of libsdv2.so: sm_100a kernels for the per-chunk causal self-attention of the
+ * causal Wan DiT used by StreamDiffusionV2 (ring-buffer K/V cache with sink slots, attention
+ * over the wrapped cache, text cross-attention from a persistent K/V cache).
+ *
+ * Conventions
+ *   - every pointer named *_dev or held in an sdv2_view is a CUDA device pointer borrowed for the
+ *     duration of the call; nothing is allocated, freed or retained by the library;
+ *   - arrays documented as "host" are read during the call and copied into the launch parameters;
+ *   - `stream` is a cudaStream_t passed as void*; calls enqueue work and return without
+ *     synchronising (except sdv2_read_status);
+ *   - return value: SDV2_OK or a negative SDV2_ERR_* code; the library never aborts or traps;
+ *   - element strides are in elements of the tensor's dtype; the innermost (head_dim) stride is 1.
+ *
+ * "Reference" below is the upstream Python implementation; paths are relative to its root.
+ */
+#ifndef SDV2_H_
+#define SDV2_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SDV2_ABI_VERSION 1
+#define SDV2_MAX_ROWS 64 /* cache batch rows (denoise levels x streams) per call */
+
+enum {
+  SDV2_OK = 0,
+  SDV2_ERR_INVALID_ARG = -1,       /* null pointer, negative size, slot outside the cache ... */
+  SDV2_ERR_UNSUPPORTED_SHAPE = -2, /* head_dim != 128, too many rows ... */
+  SDV2_ERR_MISALIGNED = -3,        /* pointer or stride not 16-byte aligned */
+  SDV2_ERR_CUDA = -4,              /* a CUDA runtime/driver call failed; see sdv2_last_cuda_error */
+  SDV2_ERR_TIMEOUT = -5,           /* a bounded device-side wait ran out (reported by sdv2_read_status) */
+  SDV2_ERR_WORKSPACE = -6          /* workspace missing or too small */
+};
+
+enum { SDV2_DTYPE_BF16 = 0, SDV2_DTYPE_F32 = 1 };
+
+/* A [rows, tokens, heads, head_dim] tensor view with head_dim contiguous. stride_row may be 0
+ * (one row broadcast to all) where documented. */
+typedef struct {
+  void* ptr;
+  int64_t stride_row;
+  int64_t stride_tok;
+  int64_t stride_head;
+} sdv2_view;
+
+int sdv2_abi_version(void);
+const char* sdv2_strerror(int code);
+/* cudaError_t of the most recent failing CUDA call made by this thread through the library. */
+int sdv2_last_cuda_error(void);
+
+/*
+ * Fused 3D rotary embedding + K/V slot write.
+ *
+ * Replaces, per call of reference CausalWanSelfAttention.forward (models/wan/causal_model.py):
+ *   causal_rope_apply on q and k ............ :253-266 (-> :94-108, multiplier :57-73)
+ *   the K/V slice assignments ............... :321-322 and :336-337
+ *   the four index fill_ calls per row ...... :303-304, :341-342
+ * The slot positions themselves (dst_begin) come from the caller's integer mirror of :279-342.
+ *
+ * For every row b, token t (ordered frame-major over grid_f x grid_h x grid_w), head h:
+ *   q_out[b,t,h,:]                 = rope(q[b,t,h,:])
+ *   k_cache[b, dst_begin[b]+t,h,:] = rope(k[b,t,h,:])
+ *   v_cache[b, dst_begin[b]+t,h,:] = v[b,t,h,:]
+ * rope multiplies pair (2j,2j+1) of the head dim, as a complex number, by
+ * rope_table_dev[row_j][j] where row_j = start_frame[b]+frame(t) for the first
+ * half-2*(half/3) pairs, grid row of t for the next half/3 and grid column for the last half/3
+ * (half = head_dim/2). Arithmetic is IEEE double with separately rounded products
+ * (re = a*c - b*d, im = a*d + b*c), then rounded to float and, for bf16 storage, rounded again
+ * to bf16: bit-identical to the reference's complex128 path on CPU.
+ *
+ * rope_table_dev: device, double [table_rows][head_dim/2][2] (re, im) = the reference's
+ *   model.freqs (models/wan/causal_model.py:631-638) viewed as real.
+ * start_frame, dst_begin: host int64[rows].
+ * global_end_dev/local_end_dev: device int64[rows] index tensors of the cache dict, or NULL; when
+ *   given, global_end_val/local_end_val (host int64[rows]) are stored into them by the kernel.
+ * q_out may alias q.
+ */
+int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v,
+                        const sdv2_view* q_out, const sdv2_view* k_cache, const sdv2_view* v_cache,
+                        int rows, int new_tokens, int heads, int head_dim, int64_t cache_tokens,
+                        const double* rope_table_dev, int table_rows,
+                        int grid_f, int grid_h, int grid_w,
+                        const int64_t* start_frame, const int64_t* dst_begin,
+                        int64_t* global_end_dev, int64_t* local_end_dev,
+                        const int64_t* global_end_val, const int64_t* local_end_val,
+                        int dtype, void* stream);
+
+/*
+ * Attention of the new queries over the wrapped cache: out[b] = softmax(q[b] k[b,:L_b]^T * scale)
+ * v[b,:L_b] with L_b = seq_lens[b], no causal or window mask (the window is the cache content).
+ *
+ * Replaces flash_attn_interface.flash_attn_with_kvcache(q, k_cache, v_cache, cache_seqlens) at
+ * models/wan/causal_model.py:353-358 and its fallback attention_with_kvcache_fallback (:111-157).
+ *
+ * bf16 in, fp32 accumulate, bf16 out; head_dim must be 128. tcgen05 tensor-core kernel with
+ * TMA-staged K/V tiles. seq_lens: host int32[rows], 1 <= seq_lens[b] <= cache_tokens.
+ * workspace_dev: at least sdv2_attn_workspace_bytes() bytes, 256-byte aligned; its first word is
+ * a status flag written only when a bounded device-side wait runs out (read with sdv2_read_status;
+ * zero it once after allocation).
+ */
+int sdv2_attn_kvcache(const sdv2_view* q, const sdv2_view* k_cache, const sdv2_view* v_cache,
+                      const sdv2_view* out, int rows, int q_tokens, int heads, int head_dim,
+                      int64_t cache_tokens, const int32_t* seq_lens, float softmax_scale,
+                      void* workspace_dev, size_t workspace_bytes, void* stream);
+
+size_t sdv2_attn_workspace_bytes(int rows, int q_tokens, int heads, int head_dim);
+
+/*
+ * Text cross-attention core: every query attends all kv_tokens context slots, no mask.
+ * Replaces flash_attention(q, k, v, k_lens=None) as called from WanT2VCrossAttention.forward
+ * (models/wan/wan_base/modules/model.py:189 -> models/wan/wan_base/modules/attention.py:138-261),
+ * reading K/V straight from crossattn_cache["k"/"v"]; k/v stride_row may be 0 (the reference
+ * expands one row over the batch, models/wan/causal_stream_inference.py:227-228).
+ */
+int sdv2_cross_attn(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, const sdv2_view* out,
+                    int rows, int q_tokens, int heads, int head_dim, int kv_tokens,
+                    float softmax_scale, void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/*
+ * Same contraction as sdv2_attn_kvcache on CUDA cores (one warp per query row, fp32 math), for
+ * bf16 or fp32 tensors. It exists to check the tensor-core kernel on the device at sizes where a
+ * CPU check takes minutes, and to serve fp32 caches (the reference's CPU configuration uses fp32,
+ * models/wan/causal_model.py:115-120). out has q's dtype.
+ */
+int sdv2_attn_kvcache_simt(const sdv2_view* q, const sdv2_view* k_cache, const sdv2_view* v_cache,
+                           const sdv2_view* out, int rows, int q_tokens, int heads, int head_dim,
+                           int64_t cache_tokens, const int32_t* seq_lens, float softmax_scale,
+                           int dtype, void* stream);
+
+/* Synchronises `stream`, reads the status word at the start of a workspace and clears it.
+ * Returns SDV2_OK, SDV2_ERR_TIMEOUT (a device-side wait ran out; *detail = where) or
+ * SDV2_ERR_CUDA. */
+int sdv2_read_status(void* workspace_dev, int* detail, void* stream);
+
+/*
+ * Device self-test of the two tensor-core contractions the attention kernel is built from:
+ *   s_out[128][128] = a[128][128] * b[128][128]^T      (both operands K-major in shared memory)
+ *   o_out[128][128] = p[128][128] * v[128][128]        (p from tensor memory, v MN-major)
+ * a, b, p, v: device bf16 row-major; s_out, o_out: device float row-major. No reference
+ * counterpart; used by the tests to localise a failure.
+ */
+int sdv2_selftest_umma(const void* a_dev, const void* b_dev, const void* p_dev, const void* v_dev,
+                       float* s_out_dev, float* o_out_dev, int* status_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SDV2_H_ */

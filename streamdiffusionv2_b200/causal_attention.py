@@ -1,0 +1,191 @@
+"""Kernel-backed forwards for the two attention modules of the causal Wan DiT.
+
+`self_attention_forward` has the signature and the side effects of the reference
+`CausalWanSelfAttention.forward` (models/wan/causal_model.py:189-389) on its kv-cache branch:
+same `kv_cache` dict keys, same `evict_idx` / `sink_size` / `adapt_sink_thr` module attributes,
+same cache contents and index tensors after the call.  `cross_attention_forward` mirrors
+`WanT2VCrossAttention.forward` (models/wan/wan_base/modules/model.py:161-194) including the
+`crossattn_cache` protocol.  `install(model)` binds them onto every block of a model that has the
+reference's module layout, without touching parameters or their names.
+
+Differences from the reference are in mechanism only: one fused launch ropes q/k and writes the
+K/V slots for all rows, the slot arithmetic runs on host integers (no device read-backs), and
+attention runs in the sm_100a kernels.  There is no fallback to PyTorch attention.
+"""
+from __future__ import annotations
+
+import math
+import types
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import ops
+from .ring_state import RingState
+
+_start_cache = {}
+
+
+def host_starts(current_start, rows: int) -> List[int]:
+    """`current_start` as Python ints.  The drivers pass a device int64 tensor that they update in
+    place once per chunk; it is read back once per version and shared by all layers of a forward.
+    A sequence of ints (or a `HostStarts`) skips the read-back entirely."""
+    if isinstance(current_start, HostStarts):
+        return current_start.values
+    if isinstance(current_start, torch.Tensor):
+        key = id(current_start)
+        sig = (current_start.data_ptr(), current_start._version)
+        hit = _start_cache.get(key)
+        if hit is not None and hit[0] == sig and hit[2] is current_start:
+            return hit[1]
+        vals = [int(x) for x in current_start.reshape(-1).tolist()]
+        if len(_start_cache) > 64:
+            _start_cache.clear()
+        _start_cache[key] = (sig, vals, current_start)
+        return vals
+    if isinstance(current_start, (list, tuple)):
+        return [int(x) for x in current_start]
+    return [int(current_start)] * rows
+
+
+class HostStarts:
+    """A device tensor of chunk starts together with its host copy, for callers that already know
+    the values (avoids the one read-back per chunk)."""
+
+    def __init__(self, tensor: torch.Tensor, values: Sequence[int]):
+        self.tensor = tensor
+        self.values = [int(v) for v in values]
+
+    def __floordiv__(self, other):  # the model computes start_frame = current_start // frame_tokens
+        return HostStarts(self.tensor // other, [v // int(other) for v in self.values])
+
+    def tolist(self):
+        return list(self.values)
+
+
+def _adaptive_front(kv_cache, roped_k, v, i, sink_size, frame_tokens, thr) -> Optional[int]:
+    """Adaptive sink refresh test of row i, as the reference states it (causal_model.py:284-299);
+    data dependent, so it reads one scalar back."""
+    sink_tokens = sink_size * frame_tokens
+    k_sink = kv_cache["k"][i:i + 1, :sink_tokens].reshape(sink_size, frame_tokens, -1).mean(1)
+    k_new = roped_k[i:i + 1].reshape(1, frame_tokens, -1).mean(1)
+    k_sim = torch.cosine_similarity(k_sink, k_new, dim=-1)
+    v_sink = kv_cache["v"][i:i + 1, :sink_tokens].reshape(sink_size, frame_tokens, -1).mean(1)
+    v_new = v[i:i + 1].reshape(1, frame_tokens, -1).mean(1)
+    v_sim = torch.cosine_similarity(v_sink, v_new, dim=-1)
+    avg = (k_sim + v_sim) / 2
+    lo, arg = torch.min(avg, dim=0)
+    lo, arg = lo.item(), int(arg.item())
+    if lo < thr:
+        return (arg + 1) * frame_tokens
+    return None
+
+
+def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_start):
+    """Rope, slot write, index update and attention for already projected q/k/v [B, N, H, D].
+    Returns the attention output [B, N, H, D].  This is the part of the reference forward between
+    the qkv projection and the output projection (causal_model.py:250-384)."""
+    B, n_new, H, D = q.shape
+    f, gh, gw = (int(x) for x in grid_sizes[0].tolist())
+    frame_tokens = gh * gw
+    starts = host_starts(current_start, B)
+    if len(starts) < B:
+        raise ValueError("current_start has fewer entries than batch rows")
+    starts = starts[:B]
+    start_frames = [s // frame_tokens for s in starts]
+    table = ops.rope_table_device(freqs, q.device)
+    state = RingState.of(kv_cache)
+    index_tensors = (kv_cache["global_end_index"], kv_cache["local_end_index"])
+    sink_tokens = attn_module.sink_size * frame_tokens
+    adaptive = sink_tokens > 0 and attn_module.adapt_sink_thr > -1 and n_new <= frame_tokens
+
+    if not adaptive:
+        dst, seq_lens = state.plan(kv_cache, attn_module, starts, n_new, frame_tokens)
+        roped_q = ops.rope_kv_append(q, k, v, kv_cache["k"], kv_cache["v"], table, (f, gh, gw), start_frames,
+                                     dst, index_tensors=index_tensors,
+                                     index_values=(state.global_end, state.local_end))
+    else:
+        # the slot of row i depends on roped k and on the cache as rows < i left it: rope into a
+        # staging chunk first, then test and place row by row
+        stage_k = torch.empty_like(k, memory_format=torch.contiguous_format)
+        stage_v = torch.empty_like(v, memory_format=torch.contiguous_format)
+        roped_q = ops.rope_kv_append(q, k, v, stage_k, stage_v, table, (f, gh, gw), start_frames, [0] * B)
+        state._ensure_queues(kv_cache, attn_module)
+        seq_lens = []
+        for i in range(B):
+            front = _adaptive_front(kv_cache, stage_k, stage_v, i, attn_module.sink_size, frame_tokens,
+                                    attn_module.adapt_sink_thr)
+            b0, le = state.plan_row(kv_cache, attn_module, i, starts[i], n_new, frame_tokens, front)
+            kv_cache["k"][i, b0:b0 + n_new] = stage_k[i]
+            kv_cache["v"][i, b0:b0 + n_new] = stage_v[i]
+            seq_lens.append(le)
+        g, l = index_tensors
+        g.copy_(torch.tensor(state.global_end[:g.numel()], dtype=torch.int64), non_blocking=True)
+        l.copy_(torch.tensor(state.local_end[:l.numel()], dtype=torch.int64), non_blocking=True)
+        state._sig = RingState._signature(kv_cache)
+
+    if q.dtype == torch.bfloat16:
+        return ops.attn_kvcache(roped_q, kv_cache["k"], kv_cache["v"], seq_lens)
+    return ops.attn_kvcache_simt(roped_q, kv_cache["k"], kv_cache["v"], seq_lens)
+
+
+def self_attention_forward(self, x, seq_lens, grid_sizes, freqs, block_mask, kv_cache=None, current_start=0,
+                           current_end=0, causal_rope_cache=None):
+    """Drop-in for CausalWanSelfAttention.forward on the kv-cache path (the training branch, which
+    the streaming pipelines never take, is delegated to the original forward)."""
+    if kv_cache is None:
+        original = getattr(self, "_sdv2_original_forward", None)
+        if original is None:
+            raise RuntimeError("the kernel-backed self-attention serves the kv-cache path only")
+        return original(x, seq_lens, grid_sizes, freqs, block_mask)
+    b, s, n, d = *x.shape[:2], self.num_heads, self.head_dim
+    q = self.norm_q(self.q(x)).view(b, s, n, d)
+    k = self.norm_k(self.k(x)).view(b, s, n, d)
+    v = self.v(x).view(b, s, n, d)
+    out = cached_attention(self, q, k, v, grid_sizes, freqs, kv_cache, current_start)
+    return self.o(out.flatten(2))
+
+
+def cross_attention_forward(self, x, context, context_lens, crossattn_cache=None):
+    """Drop-in for WanT2VCrossAttention.forward: K/V of the text context are computed on the
+    first call after `is_init` was cleared and read from the cache afterwards."""
+    b, n, d = x.size(0), self.num_heads, self.head_dim
+    q = self.norm_q(self.q(x)).view(b, -1, n, d)
+    if crossattn_cache is not None:
+        if not crossattn_cache["is_init"]:
+            crossattn_cache["is_init"] = True
+            k = self.norm_k(self.k(context)).view(b, -1, n, d)
+            v = self.v(context).view(b, -1, n, d)
+            crossattn_cache["k"] = k
+            crossattn_cache["v"] = v
+        else:
+            k = crossattn_cache["k"]
+            v = crossattn_cache["v"]
+    else:
+        k = self.norm_k(self.k(context)).view(b, -1, n, d)
+        v = self.v(context).view(b, -1, n, d)
+    if context_lens is not None:
+        raise NotImplementedError("per-sample context lengths are not used on the streaming path")
+    if q.dtype == torch.bfloat16:
+        out = ops.cross_attn(q, k, v)
+    else:
+        out = ops.attn_kvcache_simt(q, k, v, [k.shape[1]] * b)
+    return self.o(out.flatten(2))
+
+
+def install(model) -> int:
+    """Bind the kernel-backed forwards onto every block of `model` (anything with a `.blocks`
+    list whose items have `.self_attn` and `.cross_attn`, as the reference CausalWanModel has).
+    Parameters, buffers and attribute names are left untouched, so checkpoints keep loading.
+    Returns the number of blocks patched."""
+    n = 0
+    for block in model.blocks:
+        sa, ca = block.self_attn, block.cross_attn
+        if not hasattr(sa, "_sdv2_original_forward"):
+            sa._sdv2_original_forward = sa.forward
+        sa.forward = types.MethodType(self_attention_forward, sa)
+        if not hasattr(sa, "evict_idx"):
+            sa.evict_idx = None
+        ca.forward = types.MethodType(cross_attention_forward, ca)
+        n += 1
+    return n

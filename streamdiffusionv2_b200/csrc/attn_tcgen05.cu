@@ -1,0 +1,448 @@
+// Attention of new queries over the K/V cache on the sm_100a tensor cores.
+//
+// One CTA per (pair of 128-row query tiles, head, cache row).  Warp roles:
+//   warp 0      TMA producer: Q tiles once, then K_j / V_j tiles through a ring of 32 KB slots
+//   warp 1      MMA issuer (one thread): S = Q K^T and O += P V with tcgen05.mma, fp32 in TMEM
+//   warps 4-7   softmax for query tile 0 (one thread per query row = one TMEM lane)
+//   warps 8-11  softmax for query tile 1
+// The two query tiles share every K/V tile and alternate on the tensor pipe, so one tile's
+// softmax overlaps the other tile's MMAs.  P (bf16) is written back into the TMEM columns of S
+// and consumed as the A operand of the P V product; V is consumed MN-major straight from the
+// [kv, d] tile the TMA delivered.  O is rescaled lazily: only when a row maximum grows by more
+// than 2^8 is the accumulator in TMEM touched, by the softmax warps themselves.
+//
+// TMEM columns (512): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i aliases S_i[0,64).
+// Shared memory: Q0 Q1 (32 KB each) | kSlots x 32 KB K/V ring | mbarriers.
+// Every tile is two TMA boxes of 64 bf16 x 128 rows with the 128-byte swizzle.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+#include "sdv2_internal.h"
+
+namespace sdv2 {
+namespace attn {
+
+constexpr int kBM = 128;   // query rows per tile
+constexpr int kBN = 128;   // kv rows per tile
+constexpr int kHD = 128;   // head dim
+constexpr uint32_t kTileBytes = kBN * kHD * 2;
+constexpr uint32_t kHalfTile = kTileBytes / 2;  // one 64-column box
+constexpr int kSlots = 5;
+constexpr int kThreads = 384;
+constexpr uint32_t kSmemQ = 0;
+constexpr uint32_t kSmemKV = 2 * kTileBytes;
+constexpr uint32_t kSmemBar = kSmemKV + kSlots * kTileBytes;
+constexpr uint32_t kSmemBytes = kSmemBar + 256 + 1024;  // + alignment slack
+
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 256;
+
+// barrier indices
+constexpr int kBarQFull = 0;                   // [2]
+constexpr int kBarKvFull = 2;                  // [kSlots]
+constexpr int kBarKvEmpty = 2 + kSlots;        // [kSlots]
+constexpr int kBarSFull = 2 + 2 * kSlots;      // [2]
+constexpr int kBarPFull = kBarSFull + 2;       // [2]
+constexpr int kBarOFull = kBarPFull + 2;       // [2]
+constexpr int kNumBars = kBarOFull + 2;
+static_assert(kNumBars * 8 + 16 <= 256, "barrier block too small");
+
+constexpr uint32_t kIdescQK = umma_idesc_bf16(kBM, kBN, false, false);
+constexpr uint32_t kIdescPV = umma_idesc_bf16(kBM, kHD, false, true);
+
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+// S[stage] = Q[stage] (128 x 128, K-major) * K_tile^T (128 x 128, K-major); 8 steps of K = 16.
+__device__ __forceinline__ void issue_qk(uint32_t tmem_s, uint32_t sq, uint32_t sk) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t off = (k >> 2) * kHalfTile + (k & 3) * 32;
+    umma_ss(tmem_s, umma_smem_desc(sq + off, 16, 1024), umma_smem_desc(sk + off, 16, 1024), kIdescQK,
+            k > 0 ? 1u : 0u);
+  }
+}
+// O[stage] (+)= P[stage] (128 x 128 bf16 in TMEM, 8 columns per K step) * V_tile (kv x d, MN-major).
+__device__ __forceinline__ void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t sv, bool accumulate) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    umma_ts(tmem_o, tmem_p + k * 8, umma_smem_desc(sv + k * 2048, kHalfTile, 1024), kIdescPV,
+            (accumulate || k > 0) ? 1u : 0u);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw);
+  const uint32_t bar0 = base + kSmemBar;
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + kSmemBar + kNumBars * 8);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kSmemBar + kNumBars * 8 + 4);
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+  const int lane = threadIdx.x & 31;
+
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int q0 = blockIdx.x * (2 * kBM);
+  const bool two_tiles = q0 + kBM < p.q_tokens;
+  const int seq_len = p.seq_lens[b];
+  const int n_kv = (seq_len + kBN - 1) / kBN;
+  const int bk = p.kv_row_broadcast ? 0 : b;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 2; ++i) mbar_init(bar(kBarQFull + i), 1);
+    for (int i = 0; i < kSlots; ++i) {
+      mbar_init(bar(kBarKvFull + i), 1);
+      mbar_init(bar(kBarKvEmpty + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(kBarSFull + i), 1);
+      mbar_init(bar(kBarPFull + i), kBM);
+      mbar_init(bar(kBarOFull + i), 1);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const int n_q = two_tiles ? 2 : 1;
+      for (int s = 0; s < n_q; ++s) {
+        mbar_expect_tx(bar(kBarQFull + s), kTileBytes);
+        tma_load_4d(base + kSmemQ + s * kTileBytes, &tm_q, bar(kBarQFull + s), 0, h, q0 + s * kBM, b);
+        tma_load_4d(base + kSmemQ + s * kTileBytes + kHalfTile, &tm_q, bar(kBarQFull + s), 64, h,
+                    q0 + s * kBM, b);
+      }
+      bool ok = true;
+      int issued = 0;
+      for (int it = 0; it < 2 * n_kv && ok; ++it) {  // even: K_{it/2}, odd: V_{it/2}
+        const int slot = it % kSlots;
+        const int use = it / kSlots;
+        if (use > 0) ok = mbar_wait(bar(kBarKvEmpty + slot), (use - 1) & 1, abort_flag, p.status, WAIT_KV_EMPTY);
+        if (!ok) break;
+        const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
+        const uint32_t dst = base + kSmemKV + slot * kTileBytes;
+        mbar_expect_tx(bar(kBarKvFull + slot), kTileBytes);
+        tma_load_4d(dst, tm, bar(kBarKvFull + slot), 0, h, (it >> 1) * kBN, bk);
+        tma_load_4d(dst + kHalfTile, tm, bar(kBarKvFull + slot), 64, h, (it >> 1) * kBN, bk);
+        issued = it + 1;
+      }
+      if (!ok) {
+        // leave no copy in flight: wait (bounded) for the tiles already requested
+        for (int it = (issued > kSlots ? issued - kSlots : 0); it < issued; ++it) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar(kBarKvFull + it % kSlots), (it / kSlots) & 1) &&
+                 clock64() - t0 < kWaitBudgetCycles) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const int n_stage = two_tiles ? 2 : 1;
+      const uint32_t sq[2] = {base + kSmemQ, base + kSmemQ + kTileBytes};
+      const uint32_t tS[2] = {tmem + kColS, tmem + kColS + 128};
+      const uint32_t tO[2] = {tmem + kColO, tmem + kColO + 128};
+      auto slot_addr = [&](int it) { return base + kSmemKV + (it % kSlots) * kTileBytes; };
+      bool ok = mbar_wait(bar(kBarKvFull + 0), 0, abort_flag, p.status, WAIT_KV_FULL);
+      for (int s = 0; s < n_stage && ok; ++s) {
+        ok = mbar_wait(bar(kBarQFull + s), 0, abort_flag, p.status, WAIT_Q_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(tS[s], sq[s], slot_addr(0));
+        umma_commit(bar(kBarSFull + s));
+      }
+      if (ok) umma_commit(bar(kBarKvEmpty + 0));
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int it_v = 2 * j + 1, it_k = 2 * j + 2;
+        const bool more = j + 1 < n_kv;
+        for (int s = 0; s < n_stage && ok; ++s) {
+          ok = mbar_wait(bar(kBarPFull + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
+          if (ok && s == 0)
+            ok = mbar_wait(bar(kBarKvFull + it_v % kSlots), (it_v / kSlots) & 1, abort_flag, p.status, WAIT_KV_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(tO[s], tS[s], slot_addr(it_v), j > 0);
+          if (s == n_stage - 1) umma_commit(bar(kBarKvEmpty + it_v % kSlots));
+          if (more) {
+            if (s == 0) {
+              ok = mbar_wait(bar(kBarKvFull + it_k % kSlots), (it_k / kSlots) & 1, abort_flag, p.status, WAIT_KV_FULL);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            issue_qk(tS[s], sq[s], slot_addr(it_k));
+            umma_commit(bar(kBarSFull + s));
+            if (s == n_stage - 1) umma_commit(bar(kBarKvEmpty + it_k % kSlots));
+          } else {
+            umma_commit(bar(kBarOFull + s));
+          }
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int stage = (warp - 4) >> 2;
+    if (stage == 0 || two_tiles) {
+      const int quad = warp & 3;
+      const int row = quad * 32 + lane;
+      const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+      const uint32_t tS = tmem + lane_base + kColS + stage * 128;
+      const uint32_t tO = tmem + lane_base + kColO + stage * 128;
+      const float scale = p.scale_log2;
+      float m_used = -INFINITY;
+      float l = 0.f;
+      bool ok = true;
+      for (int j = 0; j < n_kv; ++j) {
+        ok = mbar_wait(bar(kBarSFull + stage), j & 1, abort_flag, p.status, WAIT_S_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t s[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, s[c]);
+        tmem_wait_ld();
+        const int valid = seq_len - j * kBN;
+        if (valid < kBN) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i >= valid) s[c][i] = 0xFF800000u;  // -inf
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(s[c][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(s[c][i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(s[c][i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(s[c][i + 3]));
+          }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;
+        if (j == 0) {
+          m_used = mx;  // tile 0 always has a valid column, so mx is finite
+        } else {
+          const bool grow = mx > m_used + kRescaleThreshold;
+          if (__any_sync(0xffffffffu, grow)) {
+            const float m_new = grow ? mx : m_used;
+            const float alpha = ex2_approx(m_used - m_new);
+            m_used = m_new;
+            l *= alpha;
+            // O of this stage is idle here: P V of the previous kv tile completed before S arrived
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tO + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + c * 32, o);
+            }
+          }
+        }
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(s[c][2 * i]), scale, -m_used));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(s[c][2 * i + 1]), scale, -m_used));
+            sum0 += p0;
+            sum1 += p1;
+            pk[i] = pack_bf16x2(p0, p1);
+          }
+          tmem_st16(tS + c * 16, pk);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(kBarPFull + stage));
+        l += sum0 + sum1;
+      }
+      if (ok) {
+        ok = mbar_wait(bar(kBarOFull + stage), 0, abort_flag, p.status, WAIT_O_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.f / l;
+        const int q_row = q0 + stage * kBM + row;
+        __nv_bfloat16* op = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(b) * p.out_stride_row +
+                            static_cast<int64_t>(q_row) * p.out_stride_tok +
+                            static_cast<int64_t>(h) * p.out_stride_head;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + c * 32, o);
+          tmem_wait_ld();
+          if (q_row < p.q_tokens) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+              *reinterpret_cast<uint4*>(op + c * 32 + i * 8) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// -------------------------------------------------------------------------------------------
+// Self-test of the two contractions in isolation (128 threads, one CTA).
+// -------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128, 1)
+umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                     const __grid_constant__ CUtensorMap tm_v, const __nv_bfloat16* __restrict__ pmat,
+                     float* __restrict__ s_out, float* __restrict__ o_out, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw);
+  const uint32_t sA = base, sB = base + kTileBytes, sV = base + 2 * kTileBytes;
+  const uint32_t bar0 = base + 3 * kTileBytes;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 3 * kTileBytes + 64);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + 3 * kTileBytes + 68);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 3; ++i) mbar_init(bar0 + 8 * i, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 128;
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const int row = warp * 32 + lane;
+
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(bar0, 3 * kTileBytes);
+    tma_load_2d(sA, &tm_a, bar0, 0, 0);
+    tma_load_2d(sA + kHalfTile, &tm_a, bar0, 64, 0);
+    tma_load_2d(sB, &tm_b, bar0, 0, 0);
+    tma_load_2d(sB + kHalfTile, &tm_b, bar0, 64, 0);
+    tma_load_2d(sV, &tm_v, bar0, 0, 0);
+    tma_load_2d(sV + kHalfTile, &tm_v, bar0, 64, 0);
+    if (mbar_wait(bar0, 0, abort_flag, status, WAIT_PROBE)) {
+      tc_fence_after();
+      issue_qk(tS, sA, sB);
+      umma_commit(bar0 + 8);
+    }
+  }
+  bool ok = mbar_wait(bar0 + 8, 0, abort_flag, status, WAIT_PROBE);
+  ok = __all_sync(0xffffffffu, ok);
+  if (ok) {
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tS + lane_base + c * 32, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s_out[row * 128 + c * 32 + i] = __uint_as_float(r[i]);
+    }
+    // P row -> TMEM columns [0,64) of S, two bf16 per 32-bit column (even column in the low half)
+    const uint32_t* prow = reinterpret_cast<const uint32_t*>(pmat + row * 128);
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+      uint32_t r[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = prow[c * 32 + i];
+      tmem_st32(tS + lane_base + c * 32, r);
+    }
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && !*abort_flag) {
+    tc_fence_after();
+    issue_pv(tO, tS, sV, false);
+    umma_commit(bar0 + 16);
+  }
+  ok = mbar_wait(bar0 + 16, 0, abort_flag, status, WAIT_PROBE);
+  ok = __all_sync(0xffffffffu, ok);
+  if (ok) {
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tO + lane_base + c * 32, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o_out[row * 128 + c * 32 + i] = __uint_as_float(r[i]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+}  // namespace attn
+
+cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
+                                const AttnParams& p, cudaStream_t stream) {
+  // per device and cheap, so set on every launch rather than cached per process
+  cudaError_t attr = cudaFuncSetAttribute(attn::attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(attn::kSmemBytes));
+  if (attr != cudaSuccess) return attr;
+  dim3 grid((p.q_tokens + 2 * attn::kBM - 1) / (2 * attn::kBM), p.heads, p.rows);
+  attn::attn_fwd_kernel<<<grid, attn::kThreads, attn::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_umma_selftest(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_v,
+                                 const void* p_dev, float* s_out, float* o_out, int* status,
+                                 cudaStream_t stream) {
+  const int smem = 3 * attn::kTileBytes + 128 + 1024;
+  cudaError_t attr =
+      cudaFuncSetAttribute(attn::umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (attr != cudaSuccess) return attr;
+  attn::umma_selftest_kernel<<<1, 128, smem, stream>>>(tm_a, tm_b, tm_v,
+                                                      static_cast<const __nv_bfloat16*>(p_dev), s_out, o_out,
+                                                      status);
+  return cudaGetLastError();
+}
+
+}  // namespace sdv2

@@ -1,0 +1,52 @@
+// Launch-parameter structs and launcher prototypes shared by the kernel files and the C ABI.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/sdv2.h"
+
+namespace sdv2 {
+
+struct AppendParams {
+  sdv2_view q, k, v, q_out, k_cache, v_cache;
+  const double2* table;  // [table_rows][half] (re, im)
+  int rows, tokens, heads, head_dim, half;
+  int grid_h, grid_w;
+  int cols_t, cols_h;  // complex columns in the temporal and height groups (width gets the rest)
+  int64_t* global_end_dev;
+  int64_t* local_end_dev;
+  int64_t start_frame[SDV2_MAX_ROWS];
+  int64_t dst_begin[SDV2_MAX_ROWS];
+  int64_t global_end_val[SDV2_MAX_ROWS];
+  int64_t local_end_val[SDV2_MAX_ROWS];
+};
+
+cudaError_t launch_rope_kv_append(const AppendParams& p, int dtype, cudaStream_t stream);
+
+struct AttnParams {
+  void* out;
+  int64_t out_stride_row, out_stride_tok, out_stride_head;  // elements
+  int rows, q_tokens, heads;
+  int kv_row_broadcast;  // 1: every row reads K/V row 0 (stride-0 expand)
+  float scale_log2;      // softmax_scale * log2(e)
+  int* status;           // first word of the workspace
+  int seq_lens[SDV2_MAX_ROWS];
+};
+
+cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
+                                const AttnParams& p, cudaStream_t stream);
+
+struct SimtAttnParams {
+  sdv2_view q, k, v, out;
+  int rows, q_tokens, heads;
+  float scale;
+  int seq_lens[SDV2_MAX_ROWS];
+};
+cudaError_t launch_attn_simt(const SimtAttnParams& p, int dtype, cudaStream_t stream);
+
+cudaError_t launch_umma_selftest(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_v,
+                                 const void* p_dev, float* s_out, float* o_out, int* status,
+                                 cudaStream_t stream);
+
+}  // namespace sdv2

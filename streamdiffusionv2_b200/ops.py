@@ -1,0 +1,157 @@
+"""Tensor-level wrappers over the C ABI of libsdv2.so.
+
+Every function takes CUDA tensors, launches on the current stream of the tensors' device and does
+not synchronise.  There is no CPU or PyTorch fallback: a missing library or a failing call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Dict, Optional, Sequence, Tuple
+
+import torch
+
+from . import _native as N
+
+_workspaces: Dict[int, torch.Tensor] = {}
+_tables: Dict[Tuple[int, int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def workspace(device: torch.device) -> torch.Tensor:
+    """Per-device scratch for the attention kernels (status word first), zeroed on creation."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None:
+        nbytes = int(N.lib().sdv2_attn_workspace_bytes(N.MAX_ROWS, 1 << 20, 64, 128))
+        ws = torch.zeros(nbytes + 256, dtype=torch.uint8, device=torch.device("cuda", idx))
+        off = (-ws.data_ptr()) % 256
+        ws = ws[off:off + nbytes]
+        _workspaces[idx] = ws
+    return ws
+
+
+def rope_table_device(freqs: torch.Tensor, device: torch.device) -> torch.Tensor:
+    """complex128 [rows, head_dim/2] table (the model's `freqs`) -> float64 [rows, head_dim/2, 2]
+    on `device`, cached per source tensor."""
+    key = (id(freqs), freqs.data_ptr(), device.index if device.index is not None else -1)
+    hit = _tables.get(key)
+    if hit is not None and hit[0] is freqs:
+        return hit[1]
+    if freqs.dtype != torch.complex128:
+        raise ValueError("rope table must be complex128")
+    t = torch.view_as_real(freqs.to(device)).contiguous()
+    if len(_tables) > 16:
+        _tables.clear()
+    _tables[key] = (freqs, t)
+    return t
+
+
+def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor,
+                   v_cache: torch.Tensor, table: torch.Tensor, grid: Sequence[int],
+                   start_frames: Sequence[int], dst_begin: Sequence[int], *,
+                   q_out: Optional[torch.Tensor] = None,
+                   index_tensors: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                   index_values: Optional[Tuple[Sequence[int], Sequence[int]]] = None) -> torch.Tensor:
+    """Rope q and k, write k/v of every row into cache slot [dst_begin[b], dst_begin[b]+N).
+    q, k, v: [B, N, H, D]; caches [B, Smax, H, D]; table: float64 [rows, D/2, 2] on the device.
+    Optionally stores index_values into the (global_end, local_end) int64 device tensors.
+    Returns the roped q ([B, N, H, D], contiguous)."""
+    B, n_new, H, D = q.shape
+    if q_out is None:
+        q_out = torch.empty((B, n_new, H, D), dtype=q.dtype, device=q.device)
+    f, h, w = (int(x) for x in grid)
+    ge_dev = le_dev = None
+    ge_val = le_val = None
+    if index_tensors is not None:
+        g, l = index_tensors
+        if g.dtype != torch.int64 or l.dtype != torch.int64 or g.numel() < B or l.numel() < B:
+            raise ValueError("index tensors must be int64 with one entry per row")
+        if not (g.is_contiguous() and l.is_contiguous()):
+            raise ValueError("index tensors must be contiguous")
+        ge_dev, le_dev = g.data_ptr(), l.data_ptr()
+        ge_val, le_val = N.i64_array(index_values[0]), N.i64_array(index_values[1])
+    views = [N.view(t) for t in (q, k, v, q_out, k_cache, v_cache)]
+    rc = N.lib().sdv2_rope_kv_append(
+        *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
+        f, h, w, N.i64_array(start_frames), N.i64_array(dst_begin), ge_dev, le_dev, ge_val, le_val,
+        N.dtype_code(q.dtype), N.stream_ptr(q.device))
+    N.check(rc, "sdv2_rope_kv_append")
+    return q_out
+
+
+def attn_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: Sequence[int], *,
+                 out: Optional[torch.Tensor] = None, softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """softmax(q k^T scale) v over cache[b, :seq_lens[b]] on the tensor cores (bf16)."""
+    B, n_q, H, D = q.shape
+    if q.dtype != torch.bfloat16:
+        raise ValueError("the tensor-core attention kernel takes bf16; use attn_kvcache_simt for fp32")
+    if out is None:
+        out = torch.empty((B, n_q, H, D), dtype=q.dtype, device=q.device)
+    ws = workspace(q.device)
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
+    views = [N.view(t) for t in (q, k_cache, v_cache, out)]
+    rc = N.lib().sdv2_attn_kvcache(*[C.byref(x) for x in views], B, n_q, H, D, k_cache.shape[1],
+                                   N.i32_array(seq_lens), scale, ws.data_ptr(), ws.numel(),
+                                   N.stream_ptr(q.device))
+    N.check(rc, "sdv2_attn_kvcache")
+    return out
+
+
+def cross_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+               softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """Every query attends all k.shape[1] context slots; k/v may be stride-0 expands over rows."""
+    B, n_q, H, D = q.shape
+    if q.dtype != torch.bfloat16:
+        raise ValueError("the tensor-core attention kernel takes bf16")
+    if out is None:
+        out = torch.empty((B, n_q, H, D), dtype=q.dtype, device=q.device)
+    ws = workspace(q.device)
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
+    views = [N.view(t) for t in (q, k, v, out)]
+    rc = N.lib().sdv2_cross_attn(*[C.byref(x) for x in views], B, n_q, H, D, k.shape[1], scale,
+                                 ws.data_ptr(), ws.numel(), N.stream_ptr(q.device))
+    N.check(rc, "sdv2_cross_attn")
+    return out
+
+
+def attn_kvcache_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: Sequence[int], *,
+                      out: Optional[torch.Tensor] = None, softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """Same contraction on CUDA cores in fp32 math; bf16 or fp32 tensors."""
+    B, n_q, H, D = q.shape
+    if out is None:
+        out = torch.empty((B, n_q, H, D), dtype=q.dtype, device=q.device)
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
+    views = [N.view(t) for t in (q, k_cache, v_cache, out)]
+    rc = N.lib().sdv2_attn_kvcache_simt(*[C.byref(x) for x in views], B, n_q, H, D, k_cache.shape[1],
+                                        N.i32_array(seq_lens), scale, N.dtype_code(q.dtype),
+                                        N.stream_ptr(q.device))
+    N.check(rc, "sdv2_attn_kvcache_simt")
+    return out
+
+
+def read_status(device: torch.device) -> None:
+    """Synchronise the current stream and raise if a device-side wait ran out since the last call."""
+    ws = workspace(device)
+    detail = C.c_int(0)
+    rc = N.lib().sdv2_read_status(ws.data_ptr(), C.byref(detail), N.stream_ptr(device))
+    if rc == N.ERR_TIMEOUT:
+        raise N.NativeError(rc, "attention kernel", f"device-side wait timed out at site {detail.value & 0xFF} "
+                                                    f"(block {detail.value >> 8})")
+    N.check(rc, "sdv2_read_status")
+
+
+def selftest_umma(a: torch.Tensor, b: torch.Tensor, p: torch.Tensor, v: torch.Tensor):
+    """(a @ b^T, p @ v) for 128x128 bf16 matrices through the two tensor-core code paths."""
+    dev = a.device
+    s_out = torch.full((128, 128), float("nan"), dtype=torch.float32, device=dev)
+    o_out = torch.full((128, 128), float("nan"), dtype=torch.float32, device=dev)
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
+    ts = [t.contiguous() for t in (a, b, p, v)]
+    rc = N.lib().sdv2_selftest_umma(*[t.data_ptr() for t in ts], s_out.data_ptr(), o_out.data_ptr(),
+                                    status.data_ptr(), N.stream_ptr(dev))
+    N.check(rc, "sdv2_selftest_umma")
+    torch.cuda.synchronize(dev)
+    st = int(status[0].item())
+    if st != 0:
+        raise N.NativeError(N.ERR_TIMEOUT, "sdv2_selftest_umma", f"device-side wait timed out at site {st & 0xFF}")
+    return s_out, o_out
