@@ -1,0 +1,261 @@
+"""Host-side mirror of the causal Wan DiT interface, built on the sm_100a attention kernels.
+
+`CausalWanModel` takes the same constructor arguments, exposes the same parameter names and the
+same kv-cache forward signature as the reference model (models/wan/causal_model.py:523-651,
+700-840), so a checkpoint written for one loads into the other with strict=True and the reference
+drivers can call either.  Only the inference (kv-cache) path exists here; everything that is not
+attention is ordinary PyTorch (library GEMMs, norms), the attention modules call the kernels
+through `causal_attention`.
+
+Layout of one block (models/wan/causal_model.py:432-487): adaptive-LayerNorm modulated
+self-attention over the ring cache, text cross-attention from the persistent cache, gated FFN;
+six modulation vectors per frame come from the timestep embedding.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Union
+
+import torch
+import torch.nn as nn
+
+from . import causal_attention as CA
+
+
+def timestep_features(dim: int, t: torch.Tensor) -> torch.Tensor:
+    """[cos | sin] of t * 10000^(-i/half) in float64 (models/wan/wan_base/modules/model.py:15-26)."""
+    half = dim // 2
+    t = t.to(torch.float64)
+    freq = torch.pow(10000, -torch.arange(half, device=t.device, dtype=torch.float64) / half)
+    ang = torch.outer(t, freq)
+    return torch.cat([ang.cos(), ang.sin()], dim=1)
+
+
+def build_rope_table(head_dim: int, positions: int = 1024, theta: float = 10000.0) -> torch.Tensor:
+    """complex128 [positions, head_dim/2]: temporal, height and width column groups
+    (models/wan/causal_model.py:631-638; models/wan/wan_base/modules/model.py:29-36)."""
+    def unit(dim):
+        inv = 1.0 / torch.pow(theta, torch.arange(0, dim, 2, dtype=torch.float64) / dim)
+        ang = torch.outer(torch.arange(positions), inv)
+        return torch.polar(torch.ones_like(ang), ang)
+    d = head_dim
+    return torch.cat([unit(d - 4 * (d // 6)), unit(2 * (d // 6)), unit(2 * (d // 6))], dim=1)
+
+
+class RMSNorm(nn.Module):
+    """x / rms(x) * weight with the statistics in fp32 (model.py:70-86)."""
+
+    def __init__(self, dim: int, eps: float = 1e-5):
+        super().__init__()
+        self.dim, self.eps = dim, eps
+        self.weight = nn.Parameter(torch.ones(dim))
+
+    def forward(self, x):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + self.eps)).type_as(x) * self.weight
+
+
+class PlainLayerNorm(nn.LayerNorm):
+    """LayerNorm that returns its input's dtype (model.py:89-100)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6, elementwise_affine: bool = False):
+        super().__init__(dim, eps=eps, elementwise_affine=elementwise_affine)
+
+    def forward(self, x):
+        return super().forward(x).type_as(x)
+
+
+class _AttentionBase(nn.Module):
+    def __init__(self, dim: int, num_heads: int, qk_norm: bool = True, eps: float = 1e-6):
+        super().__init__()
+        assert dim % num_heads == 0
+        self.dim, self.num_heads, self.head_dim = dim, num_heads, dim // num_heads
+        self.qk_norm, self.eps = qk_norm, eps
+        self.q = nn.Linear(dim, dim)
+        self.k = nn.Linear(dim, dim)
+        self.v = nn.Linear(dim, dim)
+        self.o = nn.Linear(dim, dim)
+        self.norm_q = RMSNorm(dim, eps=eps) if qk_norm else nn.Identity()
+        self.norm_k = RMSNorm(dim, eps=eps) if qk_norm else nn.Identity()
+
+
+class CausalSelfAttention(_AttentionBase):
+    """Self-attention over the sink + ring K/V cache.  Carries the same mutable attributes as the
+    reference module: `sink_size`, `adapt_sink_thr`, `evict_idx` (causal_model.py:177-179)."""
+
+    def __init__(self, dim, num_heads, qk_norm=True, eps=1e-6):
+        super().__init__(dim, num_heads, qk_norm, eps)
+        self.sink_size = 3
+        self.adapt_sink_thr = -1
+        self.evict_idx = None
+
+    forward = CA.self_attention_forward
+
+
+class TextCrossAttention(_AttentionBase):
+    """Cross-attention to the text context with K/V served from `crossattn_cache`."""
+
+    forward = CA.cross_attention_forward
+
+
+class DiTBlock(nn.Module):
+    def __init__(self, dim, ffn_dim, num_heads, qk_norm=True, cross_attn_norm=False, eps=1e-6):
+        super().__init__()
+        self.norm1 = PlainLayerNorm(dim, eps)
+        self.self_attn = CausalSelfAttention(dim, num_heads, qk_norm, eps)
+        self.norm3 = PlainLayerNorm(dim, eps, elementwise_affine=True) if cross_attn_norm else nn.Identity()
+        self.cross_attn = TextCrossAttention(dim, num_heads, qk_norm, eps)
+        self.norm2 = PlainLayerNorm(dim, eps)
+        self.ffn = nn.Sequential(nn.Linear(dim, ffn_dim), nn.GELU(approximate="tanh"), nn.Linear(ffn_dim, dim))
+        self.modulation = nn.Parameter(torch.randn(1, 6, dim) / dim ** 0.5)
+
+    def forward(self, x, e, grid_sizes, freqs, context, kv_cache, crossattn_cache, current_start):
+        """x [B, L, C]; e [B, F, 6, C] (per-frame modulation from the timestep embedding)."""
+        frames = e.shape[1]
+        per_frame = x.shape[1] // frames
+        shift_a, scale_a, gate_a, shift_f, scale_f, gate_f = (self.modulation.unsqueeze(1) + e).chunk(6, dim=2)
+
+        def modulate(y, scale, shift):
+            return (y.unflatten(1, (frames, per_frame)) * (1 + scale) + shift).flatten(1, 2)
+
+        def gated(y, gate):
+            return (y.unflatten(1, (frames, per_frame)) * gate).flatten(1, 2)
+
+        y = self.self_attn(modulate(self.norm1(x), scale_a, shift_a), None, grid_sizes, freqs, None,
+                           kv_cache, current_start, None)
+        x = x + gated(y, gate_a)
+        x = x + self.cross_attn(self.norm3(x), context, None, crossattn_cache=crossattn_cache)
+        y = self.ffn(modulate(self.norm2(x), scale_f, shift_f))
+        return x + gated(y, gate_f)
+
+
+class OutputHead(nn.Module):
+    def __init__(self, dim, out_dim, patch_size, eps=1e-6):
+        super().__init__()
+        self.norm = PlainLayerNorm(dim, eps)
+        self.head = nn.Linear(dim, math.prod(patch_size) * out_dim)
+        self.modulation = nn.Parameter(torch.randn(1, 2, dim) / dim ** 0.5)
+
+    def forward(self, x, e):
+        """x [B, L, C]; e [B, F, 1, C] -> [B, F, L/F, prod(patch)*out_dim]."""
+        frames = e.shape[1]
+        shift, scale = (self.modulation.unsqueeze(1) + e).chunk(2, dim=2)
+        return self.head(self.norm(x).unflatten(1, (frames, x.shape[1] // frames)) * (1 + scale) + shift)
+
+
+def _as_ints(v) -> List[int]:
+    if isinstance(v, torch.Tensor):
+        return [int(i) for i in v.reshape(-1).tolist()]
+    if isinstance(v, (list, tuple)):
+        return [int(i) for i in v]
+    return [int(v)]
+
+
+class CausalWanModel(nn.Module):
+    """Causal Wan DiT, inference path.  `forward` keeps the reference's calling convention:
+    positional (x, t, context, seq_len) plus kv_cache / crossattn_cache / current_start /
+    current_end / block_mode / block_num / patched_x_shape keywords."""
+
+    def __init__(self, model_type="t2v", patch_size=(1, 2, 2), text_len=512, in_dim=16, dim=2048, ffn_dim=8192,
+                 freq_dim=256, text_dim=4096, out_dim=16, num_heads=16, num_layers=32, window_size=(-1, -1),
+                 qk_norm=True, cross_attn_norm=True, eps=1e-6):
+        super().__init__()
+        if model_type != "t2v":
+            raise NotImplementedError("only the text-to-video variant is used by the streaming pipelines")
+        self.model_type, self.patch_size, self.text_len = model_type, tuple(patch_size), text_len
+        self.in_dim, self.dim, self.ffn_dim, self.freq_dim = in_dim, dim, ffn_dim, freq_dim
+        self.text_dim, self.out_dim, self.num_heads, self.num_layers = text_dim, out_dim, num_heads, num_layers
+        self.eps = eps
+        self.patch_embedding = nn.Conv3d(in_dim, dim, kernel_size=self.patch_size, stride=self.patch_size)
+        self.text_embedding = nn.Sequential(nn.Linear(text_dim, dim), nn.GELU(approximate="tanh"), nn.Linear(dim, dim))
+        self.time_embedding = nn.Sequential(nn.Linear(freq_dim, dim), nn.SiLU(), nn.Linear(dim, dim))
+        self.time_projection = nn.Sequential(nn.SiLU(), nn.Linear(dim, dim * 6))
+        self.blocks = nn.ModuleList(
+            [DiTBlock(dim, ffn_dim, num_heads, qk_norm, cross_attn_norm, eps) for _ in range(num_layers)])
+        self.head = OutputHead(dim, out_dim, self.patch_size, eps)
+        head_dim = dim // num_heads
+        assert head_dim % 2 == 0
+        # plain attribute, not a buffer: .to(dtype) must not touch it (causal_model.py:630-638)
+        self.freqs = build_rope_table(head_dim)
+        self.num_frame_per_block = 1
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        """Xavier for every Linear, N(0, 0.02) for the two embedding MLPs, zero output projection
+        (causal_model.py:991-1013)."""
+        for m in self.modules():
+            if isinstance(m, nn.Linear):
+                nn.init.xavier_uniform_(m.weight)
+                if m.bias is not None:
+                    nn.init.zeros_(m.bias)
+        nn.init.xavier_uniform_(self.patch_embedding.weight.flatten(1))
+        for seq in (self.text_embedding, self.time_embedding):
+            for m in seq.modules():
+                if isinstance(m, nn.Linear):
+                    nn.init.normal_(m.weight, std=0.02)
+        nn.init.zeros_(self.head.head.weight)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, *args, **kwargs):
+        if kwargs.get("kv_cache") is None:
+            raise NotImplementedError("this model serves the kv-cache inference path only")
+        return self._forward_inference(*args, **kwargs)
+
+    def _forward_inference(self, x, t, context, seq_len, clip_fea=None, y=None, kv_cache=None, crossattn_cache=None,
+                           current_start=0, current_end=0, block_mode="input", block_num=(-1,),
+                           patched_x_shape=None):
+        """x: [B, C, F, H, W] latents ('input' mode) or [B, L, dim] activations of the previous
+        pipeline stage ('middle' / 'output'); t: [B, F] timesteps; context: [B, Lt, text_dim].
+        Returns [B, C, F, H, W], or (activations, patched_x_shape) when the stage ends before the
+        last block.  block_num = (first_block, end_block) of this stage."""
+        device = self.patch_embedding.weight.device
+        if self.freqs.device != device:
+            self.freqs = self.freqs.to(device)
+        rng = _as_ints(block_num)
+        first, last = rng[0], rng[-1]
+
+        if block_mode == "input":
+            x = self.patch_embedding(x if isinstance(x, torch.Tensor) else torch.stack(list(x)))
+            bsz, cch, frames, gh, gw = x.shape
+            patched_x_shape = torch.tensor([1, cch, frames, gh, gw], dtype=torch.int64, device=device)
+            x = x.flatten(2).transpose(1, 2)
+        else:
+            _, cch, frames, gh, gw = _as_ints(patched_x_shape)
+            if x.shape[1] != frames * gh * gw:
+                raise ValueError("stage activations do not match patched_x_shape")
+            bsz = x.shape[0]
+        grid_sizes = torch.tensor([[frames, gh, gw]] * bsz, dtype=torch.long)
+        assert x.shape[1] <= seq_len
+
+        e = self.time_embedding(timestep_features(self.freq_dim, t.flatten()).type_as(x))
+        e0 = self.time_projection(e).unflatten(1, (6, self.dim)).unflatten(0, t.shape)
+
+        ctx = context if isinstance(context, torch.Tensor) else torch.stack(
+            [torch.cat([u, u.new_zeros(self.text_len - u.size(0), u.size(1))]) for u in context])
+        if ctx.shape[1] < self.text_len:
+            ctx = torch.cat([ctx, ctx.new_zeros(ctx.shape[0], self.text_len - ctx.shape[1], ctx.shape[2])], dim=1)
+        ctx = self.text_embedding(ctx)
+
+        starts = CA.HostStarts(current_start, CA.host_starts(current_start, bsz)) \
+            if isinstance(current_start, torch.Tensor) else current_start
+
+        for idx, block in enumerate(self.blocks):
+            if block_mode in ("output", "middle") and idx < first:
+                continue
+            if block_mode in ("input", "middle") and idx == last:
+                return x, patched_x_shape
+            x = block(x, e0, grid_sizes, self.freqs, ctx, kv_cache[idx], crossattn_cache[idx], starts)
+        if block_mode == "input" and last == len(self.blocks):
+            return x, patched_x_shape
+
+        x = self.head(x, e.unflatten(0, t.shape).unsqueeze(2))
+        return self.unpatchify(x, (frames, gh, gw))
+
+    def unpatchify(self, x, grid):
+        """[B, F, gh*gw, p0*p1*p2*C] -> [B, C, F*p0, gh*p1, gw*p2]."""
+        f, gh, gw = grid
+        p0, p1, p2 = self.patch_size
+        b = x.shape[0]
+        x = x.reshape(b, f, gh, gw, p0, p1, p2, self.out_dim)
+        x = x.permute(0, 7, 1, 4, 2, 5, 3, 6)
+        return x.reshape(b, self.out_dim, f * p0, gh * p1, gw * p2)

@@ -171,3 +171,71 @@ def load_fixture(name: str):
 
 def load_traces():
     return json.load(open(os.path.join(HERE, "index_traces.json")))
+
+
+# ---------------------------------------------------------------------------------------------
+# model-level cases: a tiny causal DiT driven by the streaming scheduler
+# ---------------------------------------------------------------------------------------------
+import zlib  # noqa: E402
+
+MODEL_KW = dict(model_type="t2v", patch_size=(1, 2, 2), text_len=512, in_dim=16, dim=256, ffn_dim=512,
+                freq_dim=64, text_dim=64, out_dim=16, num_heads=2, num_layers=3, qk_norm=True,
+                cross_attn_norm=True, eps=1e-6)
+
+MODEL_CASES = {
+    # stream batch, 2 frames per chunk, 3-frame first chunk, refresh rule kicks in
+    "m_stream": dict(levels=[700, 500], frames=2, cache_frames=7, sink=1, chunks=10, latent_hw=(4, 6),
+                     refresh_at=12, seed=100),
+    # one frame per chunk with 3 sink frames, 3 levels
+    "m_stream_1f": dict(levels=[800, 600, 400], frames=1, cache_frames=6, sink=3, chunks=9, latent_hw=(4, 6),
+                        refresh_at=50, seed=101),
+    # two pipeline stages (blocks [0,2) and [2,3)), one frame per chunk
+    "m_stages": dict(levels=[700, 500], frames=1, cache_frames=6, sink=2, chunks=8, latent_hw=(4, 6),
+                     refresh_at=50, seed=102, split=2),
+}
+
+
+def seed_parameters(model) -> None:
+    """Deterministic weights keyed by parameter name, independent of construction order."""
+    with torch.no_grad():
+        for name, p in sorted(model.named_parameters()):
+            g = torch.Generator().manual_seed(zlib.crc32(name.encode()) & 0x7FFFFFFF)
+            r = torch.randn(p.shape, generator=g)
+            if name.endswith("modulation"):
+                p.copy_(0.2 * r)
+            elif p.dim() >= 2:
+                fan_in = p[0].numel()
+                p.copy_(r * (0.7 / fan_in ** 0.5))
+            elif "norm" in name and name.endswith("weight"):
+                p.copy_(1.0 + 0.1 * r)
+            else:
+                p.copy_(0.02 * r)
+
+
+def model_inputs(case: dict):
+    """Prompt embedding, first-chunk latents and per-chunk latents for a model case."""
+    g = torch.Generator().manual_seed(case["seed"])
+    h, w = case["latent_hw"]
+    prompt = torch.randn(1, 512, MODEL_KW["text_dim"], generator=g)
+    first = torch.randn(1, 1 + case["frames"], 16, h, w, generator=g)
+    chunks = [torch.randn(1, case["frames"], 16, h, w, generator=g) for _ in range(case["chunks"])]
+    return prompt, first, chunks
+
+
+def model_schedule(case: dict):
+    """(current_start, current_end) per streamed chunk, with the drivers' refresh rule
+    (streamv2v/inference.py:195-252)."""
+    h, w = case["latent_hw"]
+    fs = (h // 2) * (w // 2)
+    smax = case["cache_frames"] * fs
+    start = fs * (1 + case["frames"])
+    end = start + case["frames"] * fs
+    out = []
+    for _ in range(case["chunks"]):
+        if start // fs >= case["refresh_at"]:
+            start = smax - fs
+            end = start + case["frames"] * fs
+        out.append((start, end))
+        start = end
+        end += case["frames"] * fs
+    return fs, out

@@ -1,1 +1,116 @@
-def generate(ref, here): pass
+"""Model-level fixtures: the reference's own CausalWanModel + CausalStreamInferencePipeline on a
+tiny seeded model (CPU, fp32).  Called from make_golden.py."""
+from __future__ import annotations
+
+import os
+import types
+
+import numpy as np
+import torch
+
+import cases
+
+
+def build_reference_pipeline(ref, case, block_mode="input"):
+    model = ref.cm.CausalWanModel(**cases.MODEL_KW)
+    cases.seed_parameters(model)
+    model.eval()
+    wrapper = ref.ww.CausalWanDiffusionWrapper.__new__(ref.ww.CausalWanDiffusionWrapper)
+    torch.nn.Module.__init__(wrapper)
+    wrapper.model = model
+    wrapper.uniform_timestep = False
+    wrapper.scheduler = ref.fm.FlowMatchScheduler(shift=8.0, sigma_min=0.0, extra_one_step=True)
+    wrapper.scheduler.set_timesteps(1000, training=True)
+    wrapper.seq_len = 32760
+    wrapper.post_init()
+
+    prompt, first, chunks = cases.model_inputs(case)
+    pipe = ref.csi.CausalStreamInferencePipeline.__new__(ref.csi.CausalStreamInferencePipeline)
+    torch.nn.Module.__init__(pipe)
+    pipe.device = torch.device("cpu")
+    pipe.generator = wrapper
+    pipe.text_encoder = lambda text_prompts: {"prompt_embeds": prompt.clone()}
+    pipe.scheduler = wrapper.get_scheduler()
+    pipe.denoising_step_list = torch.tensor(case["levels"], dtype=torch.long)
+    pipe.num_transformer_blocks = cases.MODEL_KW["num_layers"]
+    pipe.num_heads = cases.MODEL_KW["num_heads"]
+    h, w = case["latent_hw"]
+    pipe.frame_seq_length = (h // 2) * (w // 2)
+    pipe.num_kv_cache = case["cache_frames"]
+    pipe.kv_cache_length = pipe.frame_seq_length * pipe.num_kv_cache
+    pipe.num_sink_tokens = case["sink"]
+    pipe.adapt_sink_threshold = -1
+    pipe.num_frame_per_block = case["frames"]
+    model.num_frame_per_block = case["frames"]
+    pipe.conditional_dict = None
+    pipe.kv_cache1 = pipe.kv_cache2 = pipe.hidden_states = pipe.block_x = None
+    pipe.args = types.SimpleNamespace()
+    return pipe
+
+
+def snapshot(pipe, layer):
+    kv = pipe.kv_cache1[layer]
+    mod = pipe.generator.model.blocks[layer].self_attn
+    return {"global_end": kv["global_end_index"].tolist(), "local_end": kv["local_end_index"].tolist(),
+            "evict_idx": [list(map(int, r)) for r in mod.evict_idx], "current_step": int(kv["current_step"]),
+            "k_sha": cases.sha(kv["k"]), "v_sha": cases.sha(kv["v"])}
+
+
+def run_stream(ref, case):
+    pipe = build_reference_pipeline(ref, case)
+    prompt, first, chunks = cases.model_inputs(case)
+    fs, sched = cases.model_schedule(case)
+    torch.manual_seed(case["seed"] + 1)
+    arrays, meta = {}, {"steps": []}
+    with torch.no_grad():
+        out0 = pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
+                            current_start=0, current_end=fs * (1 + case["frames"]))
+        arrays["prepare"] = out0.numpy().copy()
+        meta["prepare"] = {"layer0": snapshot(pipe, 0), "layerL": snapshot(pipe, len(pipe.kv_cache1) - 1)}
+        for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
+            hs = pipe.inference_stream(noise=noise, current_start=cs, current_end=ce, current_step=None)
+            arrays[f"out_{i}"] = hs.numpy().copy()
+            meta["steps"].append({"layer0": snapshot(pipe, 0), "layerL": snapshot(pipe, len(pipe.kv_cache1) - 1)})
+    return meta, arrays
+
+
+def run_stages(ref, case):
+    """Two pipeline stages in one process: stage A owns blocks [0, split), stage B the rest."""
+    split = case["split"]
+    nblk = cases.MODEL_KW["num_layers"]
+    pa = build_reference_pipeline(ref, case)
+    pb = build_reference_pipeline(ref, case)
+    prompt, first, chunks = cases.model_inputs(case)
+    fs, sched = cases.model_schedule(case)
+    arrays, meta = {}, {"steps": []}
+    with torch.no_grad():
+        for pipe, mode, rng in ((pa, "input", [0, split]), (pb, "output", [split, nblk])):
+            torch.manual_seed(case["seed"] + 1)
+            pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
+                         current_start=0, current_end=fs * (1 + case["frames"]), block_mode=mode)
+        torch.manual_seed(case["seed"] + 2)
+        noise_in = None
+        for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
+            # the last stage's re-noised rows come back to the first stage on the next chunk
+            if noise_in is not None:
+                pa.hidden_states.copy_(noise_in)
+            act, pshape = pa.inference(noise=noise, current_start=cs, current_end=ce, current_step=None,
+                                       block_mode="input", block_num=torch.tensor([0, split]))
+            den, _ = pb.inference(noise=pa.hidden_states, current_start=pa.kv_cache_starts,
+                                  current_end=pa.kv_cache_ends, current_step=None, block_mode="output",
+                                  block_num=torch.tensor([split, nblk]), patched_x_shape=pshape, block_x=act)
+            noise_in = den.clone()
+            arrays[f"act_{i}"] = act.numpy().copy()
+            arrays[f"out_{i}"] = den.numpy().copy()
+            meta["steps"].append({"stageA_layer0": snapshot(pa, 0), "stageB_layerL": snapshot(pb, nblk - 1),
+                                  "pshape": pshape.tolist()})
+    return meta, arrays
+
+
+def generate(ref, here):
+    import json
+    for name, case in cases.MODEL_CASES.items():
+        meta, arrays = (run_stages if "split" in case else run_stream)(ref, case)
+        np.savez_compressed(os.path.join(here, f"{name}.npz"),
+                            meta=np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8), **arrays)
+        print("wrote", name)

@@ -1,0 +1,111 @@
+"""Host logic of the model mirror and the streaming scheduler against fixtures recorded from the
+reference's CausalWanModel + CausalStreamInferencePipeline (CPU, fp32).  Attention arithmetic is
+supplied by the oracle through tests/fake_ops.py; what is under test is everything around it:
+parameter naming, block wiring, stage slicing, cache ownership, row shifting, index state."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import fake_ops
+from model_harness import build_pipeline, snapshot
+
+INDEX_KEYS = ("global_end", "local_end", "evict_idx", "current_step")
+
+
+def _check_state(got, want, where):
+    for k in INDEX_KEYS:
+        assert got[k] == want[k], (where, k, got[k], want[k])
+
+
+@pytest.mark.parametrize("name", ["m_stream", "m_stream_1f"])
+def test_stream_pipeline_matches_reference(name, monkeypatch):
+    fake_ops.install(monkeypatch)
+    case = cases.MODEL_CASES[name]
+    meta, z = cases.load_fixture(name)
+    pipe, first, chunks = build_pipeline(case)
+    fs, sched = cases.model_schedule(case)
+    nl = cases.MODEL_KW["num_layers"]
+    torch.manual_seed(case["seed"] + 1)
+    with torch.no_grad():
+        out0 = pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
+                            current_start=0, current_end=fs * (1 + case["frames"]))
+        assert np.abs(out0.numpy() - z["prepare"]).max() < 2e-4
+        _check_state(snapshot(pipe, 0), meta["prepare"]["layer0"], "prepare")
+        # layer 0 sees identical inputs, so its cache must match the reference bit for bit
+        assert snapshot(pipe, 0)["k_sha"] == meta["prepare"]["layer0"]["k_sha"]
+        for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
+            hs = pipe.inference_stream(noise=noise, current_start=cs, current_end=ce, current_step=None)
+            assert np.abs(hs.numpy() - z[f"out_{i}"]).max() < 5e-4, (name, i)
+            _check_state(snapshot(pipe, 0), meta["steps"][i]["layer0"], (name, i, 0))
+            _check_state(snapshot(pipe, nl - 1), meta["steps"][i]["layerL"], (name, i, nl - 1))
+
+
+def test_two_stage_pipeline_matches_reference(monkeypatch):
+    fake_ops.install(monkeypatch)
+    case = cases.MODEL_CASES["m_stages"]
+    meta, z = cases.load_fixture("m_stages")
+    split, nblk = case["split"], cases.MODEL_KW["num_layers"]
+    fs, sched = cases.model_schedule(case)
+    pa, first, chunks = build_pipeline(case)
+    pb, _, _ = build_pipeline(case)
+    with torch.no_grad():
+        for pipe, mode in ((pa, "input"), (pb, "output")):
+            torch.manual_seed(case["seed"] + 1)
+            pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
+                         current_start=0, current_end=fs * (1 + case["frames"]), block_mode=mode)
+        torch.manual_seed(case["seed"] + 2)
+        back = None
+        for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
+            if back is not None:
+                pa.hidden_states.copy_(back)
+            act, pshape = pa.inference(noise=noise, current_start=cs, current_end=ce, current_step=None,
+                                       block_mode="input", block_num=[0, split])
+            den, _ = pb.inference(noise=pa.hidden_states, current_start=pa.kv_cache_starts,
+                                  current_end=pa.kv_cache_ends, current_step=None, block_mode="output",
+                                  block_num=[split, nblk], patched_x_shape=pshape, block_x=act)
+            back = den.clone()
+            assert pshape.tolist() == meta["steps"][i]["pshape"]
+            assert np.abs(act.numpy() - z[f"act_{i}"]).max() < 5e-4, i
+            assert np.abs(den.numpy() - z[f"out_{i}"]).max() < 5e-4, i
+            _check_state(snapshot(pa, 0), meta["steps"][i]["stageA_layer0"], (i, "A"))
+            _check_state(snapshot(pb, nblk - 1), meta["steps"][i]["stageB_layerL"], (i, "B"))
+
+
+def test_parameter_names_match_reference_layout():
+    """Checkpoints written for the reference model must load with strict=True: same names/shapes."""
+    from streamdiffusionv2_b200.wan_model import CausalWanModel
+    m = CausalWanModel(**cases.MODEL_KW)
+    names = dict((n, tuple(p.shape)) for n, p in m.named_parameters())
+    for blk in range(cases.MODEL_KW["num_layers"]):
+        for sub in ("self_attn", "cross_attn"):
+            for lin in ("q", "k", "v", "o"):
+                assert names[f"blocks.{blk}.{sub}.{lin}.weight"] == (256, 256)
+            assert names[f"blocks.{blk}.{sub}.norm_q.weight"] == (256,)
+        assert names[f"blocks.{blk}.modulation"] == (1, 6, 256)
+        assert names[f"blocks.{blk}.norm3.weight"] == (256,)
+        assert names[f"blocks.{blk}.ffn.0.weight"] == (512, 256)
+    assert names["patch_embedding.weight"] == (256, 16, 1, 2, 2)
+    assert names["head.head.weight"] == (64, 256) and names["head.modulation"] == (1, 2, 256)
+    assert names["time_projection.1.weight"] == (1536, 256)
+    assert names["text_embedding.0.weight"] == (256, 64)
+    want = set(cases.load_fixture("m_stream")[0].get("param_names", [])) or None
+    if want:
+        assert set(names) == want
+
+
+def test_external_index_writes_are_picked_up(monkeypatch):
+    """A foreign writer (cache re-ownership, session tools) changes the index tensors; the host
+    mirror must notice and re-read them instead of trusting its own copy."""
+    fake_ops.install(monkeypatch)
+    from streamdiffusionv2_b200.ring_state import RingState
+    kv = {"k": torch.zeros(2, 60, 1, 128), "v": torch.zeros(2, 60, 1, 128),
+          "global_end_index": torch.tensor([12, 12]), "local_end_index": torch.tensor([12, 12]),
+          "total_steps": 2, "current_step": 2}
+    st = RingState.of(kv)
+    assert st.global_end == [12, 12]
+    kv["global_end_index"] += 6          # in-place write by someone else
+    kv["local_end_index"] = torch.tensor([18, 18])   # tensor replaced
+    st2 = RingState.of(kv)
+    assert st2.global_end == [18, 18] and st2.local_end == [18, 18]
+    assert RingState.of(kv) is st2       # no re-read while nothing changed
