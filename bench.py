@@ -1,0 +1,328 @@
+#!/usr/bin/env python
+"""Streaming-FPS benchmark of the causal Wan DiT with the sm_100a attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N = 1: random-init Wan-1.3B-shaped causal DiT (30 blocks, dim 1536, 12 heads x 128, FFN 8960),
+bf16, 480x832 video (latent 16 x 60 x 104 per frame, 1560 tokens per latent frame), text context
+512 x 4096 ~ N(0,1), 2 denoise levels batched as 2 cache rows, 2 latent frames per chunk, cache of
+1 sink + 20 ring latent frames.  The stream is first advanced until the ring is full and wrapping;
+every warm-up and timed step is then one chunk step (8 video frames) against the full cache.
+N > 1: the same model split into N contiguous block ranges, one rank per GPU, stage activations
+passed rank to rank over NCCL (one chunk in flight per stage).
+One JSON line is printed by rank 0.  `--impl reference` times the CPU restatement of the
+reference's attention path on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FRAME_TOKENS = 1560          # 30 x 52 tokens per latent frame at 480 x 832
+LATENT_HW = (60, 104)
+CACHE_FRAMES = 21            # 1 sink + 20 ring
+FRAMES_PER_CHUNK = 2
+VIDEO_FRAMES_PER_CHUNK = 4 * FRAMES_PER_CHUNK
+LEVELS = [700, 500]
+MODEL_1P3B = dict(model_type="t2v", patch_size=(1, 2, 2), text_len=512, in_dim=16, dim=1536, ffn_dim=8960,
+                  freq_dim=256, text_dim=4096, out_dim=16, num_heads=12, num_layers=30, qk_norm=True,
+                  cross_attn_norm=True, eps=1e-6)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference attention path on the host cores
+# ---------------------------------------------------------------------------------------------
+
+def cpu_attention_path(samples: int, warmup: int, q_tokens: int, budget_s: float = 150.0):
+    """Times rope + slot write + attention over the full 21-frame cache for one layer and the 2
+    cache rows of the workload (bf16 tensors, fp32 math on CPU, as the reference does there), on
+    `q_tokens` of the chunk's 3120 query tokens per row.  Returns seconds per full layer call
+    (scaled to 3120 query tokens) per sample."""
+    from oracle import causal_attention_oracle as orc
+    torch.set_num_threads(os.cpu_count() or 1)
+    H, D, B = MODEL_1P3B["num_heads"], 128, len(LEVELS)
+    smax = CACHE_FRAMES * FRAME_TOKENS
+    n_full = FRAMES_PER_CHUNK * FRAME_TOKENS
+    g = torch.Generator().manual_seed(0)
+    table = orc.rope_table(D)
+    kc = torch.randn(B, smax, H, D, generator=g).to(torch.bfloat16)
+    vc = torch.randn(B, smax, H, D, generator=g).to(torch.bfloat16)
+    q, k, v = (torch.randn(B, n_full, H, D, generator=g).to(torch.bfloat16) for _ in range(3))
+    times = []
+    t_begin = time.time()
+    for i in range(warmup + samples):
+        t0 = time.time()
+        sf = [30, 28]
+        rq = orc.rope_apply(q, (FRAMES_PER_CHUNK, 30, 52), table, sf)
+        rk = orc.rope_apply(k, (FRAMES_PER_CHUNK, 30, 52), table, sf)
+        for b, dst in enumerate((3120, 6240)):
+            kc[b, dst:dst + n_full] = rk[b]
+            vc[b, dst:dst + n_full] = v[b]
+        t_rope = time.time() - t0
+        t1 = time.time()
+        orc.attend_cache(rq[:, :q_tokens], kc, vc, [smax] * B)
+        t_att = (time.time() - t1) * (n_full / q_tokens)
+        if i >= warmup:
+            times.append(t_rope + t_att)
+        if time.time() - t_begin > budget_s and len(times) >= 1:
+            break
+    return times
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    q_tokens = 780 if args.steps > 8 else 3120
+    times = cpu_attention_path(args.steps, min(args.warmup, 1), q_tokens)
+    layer_s = statistics.mean(times)
+    chunk_s = layer_s * MODEL_1P3B["num_layers"]
+    fps = VIDEO_FRAMES_PER_CHUNK / chunk_s
+    sample = (f"attention path only (rope + slot write + attention over the full 32760-token cache), 1 of 30 "
+              f"layers, 2 cache rows, {q_tokens} of 3120 query tokens per row timed and scaled; chunk time = 30 x "
+              f"layer time; linear layers, norms and FFN not included")
+    line = {"impl": "reference", "metric": "streaming_fps_480x832_wan1.3b", "value": fps, "unit": "video frames/s",
+            "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": chunk_s * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 storage, fp32 math",
+            "data": "synthetic", "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": fps, "unit": "video frames/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": fps, "unit": "video frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus: int):
+    return {"workload": "config 2: random-init causal Wan-1.3B DiT, 480x832, 2 denoise levels (2 cache rows), "
+                        "2 latent frames per chunk, 1 sink + 20 ring frame cache, full and wrapping",
+            "tokens_per_chunk_row": FRAMES_PER_CHUNK * FRAME_TOKENS, "cache_tokens": CACHE_FRAMES * FRAME_TOKENS,
+            "cache_rows": len(LEVELS), "blocks": MODEL_1P3B["num_layers"],
+            "parallelism": "single GPU" if n_gpus == 1 else f"pipeline of {n_gpus} contiguous block ranges",
+            "l2_policy": "per-step working set (2.8 GB weights + 12 GB K/V cache) far exceeds the 126 MB L2; "
+                         "no explicit flush"}
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+
+def build_pipeline(device, n_layers_override=None):
+    from streamdiffusionv2_b200.stream_pipeline import DiffusionWrapper, StreamPipeline
+    from streamdiffusionv2_b200.wan_model import CausalWanModel
+    torch.manual_seed(0)
+    kw = dict(MODEL_1P3B)
+    if n_layers_override:
+        kw["num_layers"] = n_layers_override
+    with torch.device(device):
+        model = CausalWanModel(**kw)
+    torch.nn.init.normal_(model.head.head.weight, std=0.02)   # the stock init zeroes the output projection
+    model = model.to(dtype=torch.bfloat16).eval()
+    g = torch.Generator(device="cpu").manual_seed(1)
+    prompt = torch.randn(1, 512, kw["text_dim"], generator=g).to(device=device, dtype=torch.bfloat16)
+    pipe = StreamPipeline(DiffusionWrapper(model), lambda text_prompts: {"prompt_embeds": prompt.clone()}, LEVELS,
+                          kw["num_layers"], kw["num_heads"], FRAME_TOKENS, CACHE_FRAMES, 1, -1, FRAMES_PER_CHUNK,
+                          device=device)
+    return pipe
+
+
+class ChunkSchedule:
+    """Chunk starts as the reference's drivers advance them, with the refresh rule."""
+
+    def __init__(self):
+        self.start = FRAME_TOKENS * (1 + FRAMES_PER_CHUNK)
+        self.end = self.start + FRAMES_PER_CHUNK * FRAME_TOKENS
+
+    def next(self):
+        if self.start // FRAME_TOKENS >= 50:
+            self.start = CACHE_FRAMES * FRAME_TOKENS - FRAME_TOKENS
+            self.end = self.start + FRAMES_PER_CHUNK * FRAME_TOKENS
+        cur = (self.start, self.end)
+        self.start = self.end
+        self.end += FRAMES_PER_CHUNK * FRAME_TOKENS
+        return cur
+
+
+def run_single_gpu(args):
+    from streamdiffusionv2_b200 import ops
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks = measured_peaks()
+    pipe = build_pipeline(device)
+    g = torch.Generator(device="cpu").manual_seed(2)
+    h, w = LATENT_HW
+    first = torch.randn(1, 1 + FRAMES_PER_CHUNK, 16, h, w, generator=g).to(device=device, dtype=torch.bfloat16)
+    n_host = 8
+    host_chunks = [torch.randn(1, FRAMES_PER_CHUNK, 16, h, w, generator=g).to(torch.bfloat16).pin_memory()
+                   for _ in range(n_host)]
+    dev_chunks = [c.to(device) for c in host_chunks]
+    host_out = torch.empty(FRAMES_PER_CHUNK, 16, h, w, dtype=torch.bfloat16).pin_memory()
+    sched = ChunkSchedule()
+
+    with torch.no_grad():
+        pipe.prepare(text_prompts=["synthetic"], device=device, dtype=torch.bfloat16, noise=first, current_start=0,
+                     current_end=FRAME_TOKENS * (1 + FRAMES_PER_CHUNK))
+        fill = 0
+        while min(pipe.kv_cache1[0]["_sdv2_host"].local_end) < CACHE_FRAMES * FRAME_TOKENS or fill < 11:
+            cs, ce = sched.next()
+            pipe.inference_stream(dev_chunks[fill % n_host], cs, ce)
+            fill += 1
+        for i in range(args.warmup):
+            cs, ce = sched.next()
+            pipe.inference_stream(dev_chunks[i % n_host], cs, ce)
+        torch.cuda.synchronize()
+        ops.read_status(device)
+
+        # ---- timed region 1: inputs resident in HBM
+        log = ops.LaunchLog(timed=True)
+        ops.set_launch_log(log)
+        sampler = ClockSampler(0)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(args.steps):
+            cs, ce = sched.next()
+            pipe.inference_stream(dev_chunks[i % n_host], cs, ce)
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        ops.set_launch_log(None)
+        ms = e0.elapsed_time(e1)
+        ops.read_status(device)
+
+        # ---- timed region 2: host buffers in, host result out, every step
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e2.record()
+        for i in range(args.steps):
+            cs, ce = sched.next()
+            x = host_chunks[i % n_host].to(device, non_blocking=True)
+            out = pipe.inference_stream(x, cs, ce)
+            host_out.copy_(out[-1], non_blocking=True)
+        e3.record()
+        torch.cuda.synchronize()
+        ms_e2e = e2.elapsed_time(e3)
+        ops.read_status(device)
+
+    launches = sum(log.counts.values())
+    att = log.durations_ms("attn_kvcache")
+    app = log.durations_ms("rope_kv_append")
+    att_ms = statistics.mean(att)
+    att_flops = log.work["attn_kvcache"] / log.counts["attn_kvcache"]
+    app_ms = statistics.mean(app)
+    app_bytes = log.work["rope_kv_append"] / log.counts["rope_kv_append"]
+    fps = VIDEO_FRAMES_PER_CHUNK * args.steps / (ms / 1e3)
+    fps_e2e = VIDEO_FRAMES_PER_CHUNK * args.steps / (ms_e2e / 1e3)
+    achieved = att_flops / (att_ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops_sustained"]
+    cpu = None
+    if not args.no_cpu_baseline:
+        times = cpu_attention_path(3, 1, 780, budget_s=40.0)
+        layer_s = statistics.mean(times)
+        cpu = {"value": VIDEO_FRAMES_PER_CHUNK / (layer_s * MODEL_1P3B["num_layers"]), "unit": "video frames/s",
+               "cores": os.cpu_count() or 1, "kind": "port",
+               "sample": f"attention path only, 1 of 30 layers, 2 cache rows, 780 of 3120 query tokens per row timed "
+                         f"and scaled, {len(times)} samples; chunk time = 30 x layer time; linear layers not included"}
+    line = {
+        "metric": "streaming_fps_480x832_wan1.3b", "value": fps, "unit": "video frames/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(1),
+        "e2e": {"value": fps_e2e, "unit": "video frames/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": host_chunks[0].numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},
+        "gpu_launches": launches, "gpu_launches_by_kernel": log.counts,
+        "roofline": {"kernel": "attn_kvcache (tcgen05)", "bound": "tensor", "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
+                     "traffic": None, "avg_launch_ms": att_ms, "flops_per_launch": att_flops,
+                     "share_of_step": att_ms * log.counts["attn_kvcache"] / ms},
+        "roofline_append": {"kernel": "rope_kv_append", "bound": "hbm", "achieved": app_bytes / (app_ms * 1e-3) / 1e9,
+                            "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": app_bytes / (app_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                            "avg_launch_ms": app_ms, "bytes_per_launch": app_bytes, "traffic": None},
+        "cpu_baseline": cpu, "clocks": clocks,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=24)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        return run_single_gpu(args)
+    from streamdiffusionv2_b200 import pipeline_bench
+    return pipeline_bench.run(args, sys.modules[__name__])
+
+
+if __name__ == "__main__":
+    main()

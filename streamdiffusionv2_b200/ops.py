@@ -17,6 +17,51 @@ _workspaces: Dict[int, torch.Tensor] = {}
 _tables: Dict[Tuple[int, int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
+class LaunchLog:
+    """Optional per-launch record for measurements: counts launches per entry point and, when
+    `timed` is set, brackets each launch with CUDA events on the launching stream.  Off unless a
+    caller installs one with `set_launch_log`."""
+
+    def __init__(self, timed: bool = False):
+        self.timed = timed
+        self.counts: Dict[str, int] = {}
+        self.events: Dict[str, list] = {}
+        self.work: Dict[str, float] = {}
+
+    def durations_ms(self, name: str):
+        return [a.elapsed_time(b) for a, b in self.events.get(name, [])]
+
+
+_log: Optional[LaunchLog] = None
+
+
+def set_launch_log(log: Optional[LaunchLog]) -> None:
+    global _log
+    _log = log
+
+
+class _Logged:
+    __slots__ = ("name", "work", "ev")
+
+    def __init__(self, name: str, work: float = 0.0):
+        self.name, self.work, self.ev = name, work, None
+
+    def __enter__(self):
+        if _log is not None:
+            _log.counts[self.name] = _log.counts.get(self.name, 0) + 1
+            _log.work[self.name] = _log.work.get(self.name, 0.0) + self.work
+            if _log.timed:
+                self.ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                self.ev[0].record()
+        return self
+
+    def __exit__(self, *exc):
+        if self.ev is not None:
+            self.ev[1].record()
+            _log.events.setdefault(self.name, []).append(self.ev)
+        return False
+
+
 def workspace(device: torch.device) -> torch.Tensor:
     """Per-device scratch for the attention kernels (status word first), zeroed on creation."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
@@ -71,10 +116,11 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
         ge_dev, le_dev = g.data_ptr(), l.data_ptr()
         ge_val, le_val = N.i64_array(index_values[0]), N.i64_array(index_values[1])
     views = [N.view(t) for t in (q, k, v, q_out, k_cache, v_cache)]
-    rc = N.lib().sdv2_rope_kv_append(
-        *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
-        f, h, w, N.i64_array(start_frames), N.i64_array(dst_begin), ge_dev, le_dev, ge_val, le_val,
-        N.dtype_code(q.dtype), N.stream_ptr(q.device))
+    with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
+        rc = N.lib().sdv2_rope_kv_append(
+            *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
+            f, h, w, N.i64_array(start_frames), N.i64_array(dst_begin), ge_dev, le_dev, ge_val, le_val,
+            N.dtype_code(q.dtype), N.stream_ptr(q.device))
     N.check(rc, "sdv2_rope_kv_append")
     return q_out
 
@@ -90,9 +136,10 @@ def attn_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     ws = workspace(q.device)
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
     views = [N.view(t) for t in (q, k_cache, v_cache, out)]
-    rc = N.lib().sdv2_attn_kvcache(*[C.byref(x) for x in views], B, n_q, H, D, k_cache.shape[1],
-                                   N.i32_array(seq_lens), scale, ws.data_ptr(), ws.numel(),
-                                   N.stream_ptr(q.device))
+    with _Logged("attn_kvcache", 4.0 * n_q * D * H * float(sum(int(x) for x in seq_lens[:B]))):
+        rc = N.lib().sdv2_attn_kvcache(*[C.byref(x) for x in views], B, n_q, H, D, k_cache.shape[1],
+                                       N.i32_array(seq_lens), scale, ws.data_ptr(), ws.numel(),
+                                       N.stream_ptr(q.device))
     N.check(rc, "sdv2_attn_kvcache")
     return out
 
@@ -108,8 +155,9 @@ def cross_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, out: Option
     ws = workspace(q.device)
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
     views = [N.view(t) for t in (q, k, v, out)]
-    rc = N.lib().sdv2_cross_attn(*[C.byref(x) for x in views], B, n_q, H, D, k.shape[1], scale,
-                                 ws.data_ptr(), ws.numel(), N.stream_ptr(q.device))
+    with _Logged("cross_attn", 4.0 * B * n_q * D * H * k.shape[1]):
+        rc = N.lib().sdv2_cross_attn(*[C.byref(x) for x in views], B, n_q, H, D, k.shape[1], scale,
+                                     ws.data_ptr(), ws.numel(), N.stream_ptr(q.device))
     N.check(rc, "sdv2_cross_attn")
     return out
 
