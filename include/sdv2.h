@@ -78,7 +78,10 @@ int sdv2_last_cuda_error(void);
  * start_frame, dst_begin: host int64[rows].
  * global_end_dev/local_end_dev: device int64[rows] index tensors of the cache dict, or NULL; when
  *   given, global_end_val/local_end_val (host int64[rows]) are stored into them by the kernel.
- * q_out may alias q.
+ * status_dev: optional device int (NULL to skip); written only if a bounded device-side wait of
+ *   the staging pipeline runs out, in the format sdv2_read_status decodes. The attention
+ *   workspace's first word may be passed.
+ * q_out, k_cache and v_cache must not overlap q, k or v.
  */
 int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v,
                         const sdv2_view* q_out, const sdv2_view* k_cache, const sdv2_view* v_cache,
@@ -88,7 +91,7 @@ int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view*
                         const int64_t* start_frame, const int64_t* dst_begin,
                         int64_t* global_end_dev, int64_t* local_end_dev,
                         const int64_t* global_end_val, const int64_t* local_end_val,
-                        int dtype, void* stream);
+                        int dtype, int* status_dev, void* stream);
 
 /*
  * Attention of the new queries over the wrapped cache: out[b] = softmax(q[b] k[b,:L_b]^T * scale)

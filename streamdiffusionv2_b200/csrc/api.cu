@@ -155,7 +155,8 @@ int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view*
                         int head_dim, int64_t cache_tokens, const double* rope_table_dev, int table_rows,
                         int grid_f, int grid_h, int grid_w, const int64_t* start_frame,
                         const int64_t* dst_begin, int64_t* global_end_dev, int64_t* local_end_dev,
-                        const int64_t* global_end_val, const int64_t* local_end_val, int dtype, void* stream) {
+                        const int64_t* global_end_val, const int64_t* local_end_val, int dtype, int* status_dev,
+                        void* stream) {
   if (rows <= 0 || new_tokens <= 0 || heads <= 0 || cache_tokens <= 0 || table_rows <= 0) return SDV2_ERR_INVALID_ARG;
   if (grid_f <= 0 || grid_h <= 0 || grid_w <= 0) return SDV2_ERR_INVALID_ARG;
   if (static_cast<int64_t>(grid_f) * grid_h * grid_w != new_tokens) return SDV2_ERR_INVALID_ARG;
@@ -200,6 +201,7 @@ int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view*
   p.cols_h = p.half / 3;
   p.global_end_dev = global_end_dev;
   p.local_end_dev = local_end_dev;
+  p.status = status_dev;
   cudaError_t e = sdv2::launch_rope_kv_append(p, dtype, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? SDV2_OK : cuda_fail(e);
 }

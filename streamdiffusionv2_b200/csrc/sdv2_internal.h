@@ -14,6 +14,11 @@ struct AppendParams {
   int rows, tokens, heads, head_dim, half;
   int grid_h, grid_w;
   int cols_t, cols_h;  // complex columns in the temporal and height groups (width gets the rest)
+  // filled in by the launcher
+  int plane;                // grid_h * grid_w
+  uint32_t magic_plane, magic_w, magic_row_vecs, magic_vph;  // ceil(2^32 / d) for exact n / d
+  int tile_tokens;          // tokens per shared-memory stage (staged kernel)
+  int* status;              // optional device word that records an abandoned wait
   int64_t* global_end_dev;
   int64_t* local_end_dev;
   int64_t start_frame[SDV2_MAX_ROWS];

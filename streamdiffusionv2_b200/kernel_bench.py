@@ -1,0 +1,154 @@
+"""Micro-benchmark of the cache kernels on synthetic bf16 q/k/v ~ N(0,1) (seed 0).
+
+    python -m streamdiffusionv2_b200.kernel_bench --kernel append --rows 2 --heads 12
+    python -m streamdiffusionv2_b200.kernel_bench --kernel attn --rows 1 --heads 12 --window-frames 21
+    python -m streamdiffusionv2_b200.kernel_bench --sweep            # window x heads x rows x chunk grid
+
+Prints one JSON line per configuration: time per launch (CUDA events on the launching stream,
+L2 flushed between launches by writing a 256 MB buffer), append GB/s (6 x rows x tokens x heads x
+128 x 2 bytes per launch) and attention TFLOP/s (4 x tokens x 128 x heads x sum of cache lengths).
+`--check-index-run STEPS` additionally drives the slot state for STEPS chunks with the drivers'
+refresh rule and compares the device index tensors with the host mirror at every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+
+import torch
+
+FRAME_TOKENS = 1560
+
+
+def _time(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return statistics.median(out), min(out)
+
+
+def run_config(kernel, rows, heads, window_frames, chunk_frames, iters, warmup, flush_l2=True):
+    from . import ops
+    from .wan_model import build_rope_table
+    dev = torch.device("cuda")
+    D = 128
+    n = chunk_frames * FRAME_TOKENS
+    s = window_frames * FRAME_TOKENS
+    g = torch.Generator(device="cpu").manual_seed(0)
+    mk = lambda *shape: torch.randn(*shape, generator=g).to(torch.bfloat16).to(dev)
+    q, k, v = mk(rows, n, heads, D), mk(rows, n, heads, D), mk(rows, n, heads, D)
+    kc = torch.randn(rows, s, heads, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn(rows, s, heads, D, device=dev, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush_l2 else None
+    res = {"kernel": kernel, "rows": rows, "heads": heads, "window_frames": window_frames,
+           "chunk_frames": chunk_frames}
+    if kernel == "append":
+        table = ops.rope_table_device(build_rope_table(D), dev)
+        dst = [min(FRAME_TOKENS, s - n)] * rows
+        fn = lambda: ops.rope_kv_append(q, k, v, kc, vc, table, (chunk_frames, 30, 52), [7] * rows, dst, q_out=out)
+        med, best = _time(fn, iters, warmup, flush)
+        nbytes = 6.0 * rows * n * heads * D * 2
+        res.update(ms=med, ms_best=best, gbs=nbytes / med / 1e6, bytes_per_launch=nbytes)
+    elif kernel == "attn":
+        fn = lambda: ops.attn_kvcache(q, kc, vc, [s] * rows, out=out)
+        med, best = _time(fn, iters, warmup, flush)
+        fl = 4.0 * rows * n * s * D * heads
+        res.update(ms=med, ms_best=best, tflops=fl / med / 1e9, flops_per_launch=fl)
+    elif kernel == "cross":
+        ck = mk(1, 512, heads, D).expand(rows, -1, -1, -1)
+        cv = mk(1, 512, heads, D).expand(rows, -1, -1, -1)
+        fn = lambda: ops.cross_attn(q, ck, cv, out=out)
+        med, best = _time(fn, iters, warmup, flush)
+        fl = 4.0 * rows * n * 512 * D * heads
+        res.update(ms=med, ms_best=best, tflops=fl / med / 1e9, flops_per_launch=fl)
+    else:
+        raise ValueError(kernel)
+    ops.read_status(dev)
+    return res
+
+
+def check_index_run(rows, heads, window_frames, chunk_frames, steps):
+    """Long wraparound run of the slot logic through the append kernel: device index tensors must
+    equal the host mirror after every step, and every slot must stay inside the cache."""
+    from . import ops
+    from .ring_state import RingState
+    from .wan_model import build_rope_table
+    dev = torch.device("cuda")
+    D, n, s = 128, chunk_frames * FRAME_TOKENS, window_frames * FRAME_TOKENS
+
+    class Mod:
+        sink_size, adapt_sink_thr, evict_idx = 1, -1, None
+
+    mod = Mod()
+    kv = {"k": torch.zeros(rows, s, heads, D, dtype=torch.bfloat16, device=dev),
+          "v": torch.zeros(rows, s, heads, D, dtype=torch.bfloat16, device=dev),
+          "global_end_index": torch.zeros(rows, dtype=torch.long, device=dev),
+          "local_end_index": torch.zeros(rows, dtype=torch.long, device=dev), "total_steps": 1, "current_step": 1}
+    table = ops.rope_table_device(build_rope_table(D), dev)
+    q = torch.randn(rows, n, heads, D, device=dev, dtype=torch.bfloat16)
+    start, bad = 0, 0
+    history = [0] * rows
+    for step in range(steps):
+        if start // FRAME_TOKENS >= 50:
+            start = s - FRAME_TOKENS
+        history = [start] + history[:-1]
+        st = RingState.of(kv)
+        dst, lens = st.plan(kv, mod, history, n, FRAME_TOKENS)
+        ops.rope_kv_append(q, q, q, kv["k"], kv["v"], table, (chunk_frames, 30, 52),
+                           [h // FRAME_TOKENS for h in history], dst,
+                           index_tensors=(kv["global_end_index"], kv["local_end_index"]),
+                           index_values=(st.global_end, st.local_end))
+        if step % 50 == 49 or step == steps - 1:
+            if kv["global_end_index"].tolist() != st.global_end or kv["local_end_index"].tolist() != st.local_end:
+                bad += 1
+        start += n
+    ops.read_status(dev)
+    return {"check": "index_run", "rows": rows, "window_frames": window_frames, "chunk_frames": chunk_frames,
+            "steps": steps, "mismatches": bad}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="attn", choices=["append", "attn", "cross"])
+    ap.add_argument("--rows", type=int, default=2)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--window-frames", type=int, default=21)
+    ap.add_argument("--chunk-frames", type=int, default=2)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--check-index-run", type=int, default=0)
+    a = ap.parse_args(argv)
+    if a.check_index_run:
+        print(json.dumps(check_index_run(a.rows, a.heads, a.window_frames, a.chunk_frames, a.check_index_run)))
+        return
+    if not a.sweep:
+        print(json.dumps(run_config(a.kernel, a.rows, a.heads, a.window_frames, a.chunk_frames, a.iters, a.warmup,
+                                    not a.no_flush)))
+        return
+    for heads in (12, 40):
+        for window in (4, 8, 16, 32):
+            for rows in (1, 4, 16):
+                if rows * window * FRAME_TOKENS * heads * 128 * 2 * 2 > 60e9:
+                    continue
+                for chunk in (1, 2, 3):
+                    for kernel in ("append", "attn"):
+                        print(json.dumps(run_config(kernel, rows, heads, window, chunk, 5, 2)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -120,7 +120,7 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
         rc = N.lib().sdv2_rope_kv_append(
             *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
             f, h, w, N.i64_array(start_frames), N.i64_array(dst_begin), ge_dev, le_dev, ge_val, le_val,
-            N.dtype_code(q.dtype), N.stream_ptr(q.device))
+            N.dtype_code(q.dtype), workspace(q.device).data_ptr(), N.stream_ptr(q.device))
     N.check(rc, "sdv2_rope_kv_append")
     return q_out
 

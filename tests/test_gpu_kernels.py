@@ -187,6 +187,55 @@ def test_rope_append_full_size_bitexact():
     assert ge.tolist() == [11, 22] and le.tolist() == [33, 44]
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rope_append_padded_heads_take_the_direct_kernel(dtype):
+    """Heads that are not back to back in memory (a slice of a wider last dimension) cannot be
+    staged as whole token rows; the per-vector kernel serves them, with the same bits."""
+    ops = _ops()
+    B, N, H, D, S = 2, 24, 3, 128, 60
+    g = torch.Generator().manual_seed(4)
+    wide = [torch.randn(B, N, H, 2 * D, generator=g).to(dtype) for _ in range(3)]
+    q, k, v = (w[..., :D] for w in wide)
+    table = orc.rope_table(D)
+    kc = torch.zeros(B, S, H, D, dtype=dtype, device="cuda")
+    vc = torch.zeros(B, S, H, D, dtype=dtype, device="cuda")
+    tdev = ops.rope_table_device(table, torch.device("cuda"))
+    rq = ops.rope_kv_append(*(w.cuda()[..., :D] for w in wide), kc, vc, tdev, (2, 3, 4), [5, 900], [0, 36])
+    rq_ref = orc.rope_apply(q.contiguous(), (2, 3, 4), table, [5, 900])
+    rk_ref = orc.rope_apply(k.contiguous(), (2, 3, 4), table, [5, 900])
+    assert cases.sha(rq) == cases.sha(rq_ref)
+    assert cases.sha(kc[0, :N]) == cases.sha(rk_ref[0]) and cases.sha(kc[1, 36:]) == cases.sha(rk_ref[1])
+    assert cases.sha(vc[1, 36:]) == cases.sha(v[1].contiguous())
+
+
+def test_rope_append_special_values_bitexact():
+    """Zeros, subnormals, infinities and NaNs in q/k go through the hardware conversion path and
+    still match the oracle bit for bit (NaN payloads excepted: compared as NaN)."""
+    ops = _ops()
+    B, N, H, D, S = 1, 12, 2, 128, 12
+    g = torch.Generator().manual_seed(6)
+    q, k, v = (torch.randn(B, N, H, D, generator=g) for _ in range(3))
+    for t in (q, k):
+        flat = t.view(-1)
+        flat[0::7] = 0.0
+        flat[1::11] = -0.0
+        flat[2::13] = 1e-39           # subnormal in bf16 and fp32
+        flat[3::17] = float("inf")
+        flat[4::19] = float("nan")
+    q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
+    table = orc.rope_table(D)
+    kc = torch.zeros(B, S, H, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    rq = ops.rope_kv_append(q.cuda(), k.cuda(), v.cuda(), kc, vc, ops.rope_table_device(table, torch.device("cuda")),
+                            (2, 2, 3), [3], [0]).cpu()
+    rq_ref = orc.rope_apply(q, (2, 2, 3), table, [3])
+    rk_ref = orc.rope_apply(k, (2, 2, 3), table, [3])
+    for got, ref in ((rq, rq_ref), (kc.cpu(), rk_ref)):
+        nan = torch.isnan(ref)
+        assert torch.equal(torch.isnan(got), nan)
+        assert torch.equal(got.view(torch.int16)[~nan], ref.view(torch.int16)[~nan])
+
+
 def test_rope_append_rejects_bad_slots():
     from streamdiffusionv2_b200 import _native
     ops = _ops()
