@@ -5,9 +5,9 @@
 // Staged kernel (the default): persistent CTAs, one per SM.  A producer warp streams whole token
 // rows of q, k and v into a ring of shared-memory stages with bulk asynchronous copies
 // (cp.async.bulk, completion counted on an mbarrier), so memory latency is hidden by the copy
-// engine instead of by registers; 16 consumer warps rope q and k out of shared memory in fp64
-// and write q_out / K slot / V slot with 16-byte coalesced stores.  Tokens are split evenly
-// over the CTAs (to within one token).
+// engine instead of by registers, and builds each tile's per-token rope multiplier rows next to
+// them.  The consumer warps rope q and k out of shared memory in fp64 and write q_out / K slot /
+// V slot with 16-byte coalesced stores.  Tokens are split evenly over the CTAs (to within one).
 //
 // Direct kernel: one thread per 16-byte vector straight from global memory; used when a token
 // row is not one contiguous run of heads or is too large for a stage.
@@ -24,23 +24,6 @@ namespace sdv2 {
 // arithmetic shared by both kernels
 // ------------------------------------------------------------------------------------------
 
-// True when one of the two bf16 in `w` has an all-zero or all-one exponent (zero, subnormal,
-// inf, nan): those take the hardware conversion instead of the integer rebuild below.
-__device__ __forceinline__ uint32_t bf16x2_special(uint32_t w) {
-  // (exp + 1) & 0xFE == 0  <=>  exp in {0, 255}; then the classic zero-halfword test
-  const uint32_t v = ((w & 0x7F807F80u) + 0x00800080u) & 0x7F007F00u;
-  return (v - 0x00010001u) & ~v & 0x80008000u;
-}
-// bf16 (normal) in the low / high half of w -> double, exactly, with integer ops only.
-__device__ __forceinline__ double bf16lo_to_f64_normal(uint32_t w) {
-  const uint32_t hi = ((((w << 13) & 0x0FFFE000u) + 0x38000000u)) | ((w << 16) & 0x80000000u);
-  return __hiloint2double(static_cast<int>(hi), 0);
-}
-__device__ __forceinline__ double bf16hi_to_f64_normal(uint32_t w) {
-  const uint32_t hi = ((((w >> 3) & 0x0FFFE000u) + 0x38000000u)) | (w & 0x80000000u);
-  return __hiloint2double(static_cast<int>(hi), 0);
-}
-
 // (a + ib) * (c + id) with every product and sum rounded separately, as the reference's CPU
 // complex128 multiply does; then fp64 -> fp32 (RN).  bf16 storage adds a second RNE step.
 __device__ __forceinline__ void rope_pair(double a, double b, double2 cs, float& re, float& im) {
@@ -51,24 +34,19 @@ __device__ __forceinline__ void rope_pair(double a, double b, double2 cs, float&
 template <typename T>
 struct Vec;  // one 16-byte vector of T
 
+// bf16 -> fp32 is a 16-bit shift; fp32 -> fp64 uses the hardware conversion, which is exact for
+// every input class (zeros, subnormals, infinities, NaNs).  Rebuilding the double with integer
+// ops was measured slower: it costs ~3x the issue slots and needs a special-value test.
 template <>
 struct Vec<__nv_bfloat16> {
   static constexpr int kPairs = 4;
   __device__ __forceinline__ static uint4 rope(uint4 x, const double2 (&cs)[4]) {
     uint32_t w[4] = {x.x, x.y, x.z, x.w};
-    const uint32_t special = bf16x2_special(w[0]) | bf16x2_special(w[1]) | bf16x2_special(w[2]) | bf16x2_special(w[3]);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      double a, b;
-      if (special == 0) {
-        a = bf16lo_to_f64_normal(w[i]);
-        b = bf16hi_to_f64_normal(w[i]);
-      } else {
-        a = static_cast<double>(__uint_as_float(w[i] << 16));
-        b = static_cast<double>(__uint_as_float(w[i] & 0xFFFF0000u));
-      }
       float re, im;
-      rope_pair(a, b, cs[i], re, im);
+      rope_pair(static_cast<double>(__uint_as_float(w[i] << 16)),
+                static_cast<double>(__uint_as_float(w[i] & 0xFFFF0000u)), cs[i], re, im);
       w[i] = pack_bf16x2(re, im);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
@@ -89,18 +67,12 @@ struct Vec<float> {
 };
 
 // n / d for n * d < 2^32 with m = ceil(2^32 / d)
-__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t m) { return __umulhi(n, m); }
+__device__ __forceinline__ int fast_div(uint32_t n, uint32_t m) { return static_cast<int>(__umulhi(n, m)); }
 
-// rope multipliers of vector column c of a token at (table row for time, grid row, grid column)
-template <int kPairs>
-__device__ __forceinline__ void load_cs(const AppendParams& p, int c, int64_t trow, int y, int x,
-                                        double2 (&cs)[kPairs]) {
-#pragma unroll
-  for (int i = 0; i < kPairs; ++i) {
-    const int j = c * kPairs + i;  // complex column inside the head
-    const int64_t row = j < p.cols_t ? trow : (j < p.cols_t + p.cols_h ? y : x);
-    cs[i] = __ldg(p.table + row * p.half + j);
-  }
+// table entry for complex column `col` of a token at (time row, grid row y, grid column x)
+__device__ __forceinline__ double2 table_entry(const AppendParams& p, int col, int64_t trow, int y, int x) {
+  const int64_t row = col < p.cols_t ? trow : (col < p.cols_t + p.cols_h ? y : x);
+  return __ldg(p.table + row * p.half + col);
 }
 
 __device__ __forceinline__ void write_index(const AppendParams& p) {
@@ -133,7 +105,8 @@ __global__ void __launch_bounds__(256) rope_kv_append_direct_kernel(const __grid
   const int y = fast_div(rem, p.magic_w);
   const int x = rem - y * p.grid_w;
   double2 cs[kPairs];
-  load_cs<kPairs>(p, c, p.start_frame[b] + f, y, x, cs);
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) cs[i] = table_entry(p, c * kPairs + i, p.start_frame[b] + f, y, x);
   const int64_t slot = p.dst_begin[b] + t;
   const int e0 = c * kElems;
   const T* qp = static_cast<const T*>(p.q.ptr) + b * p.q.stride_row + t * p.q.stride_tok + h * p.q.stride_head + e0;
@@ -154,13 +127,15 @@ __global__ void __launch_bounds__(256) rope_kv_append_direct_kernel(const __grid
 // staged kernel
 // ------------------------------------------------------------------------------------------
 namespace staged {
-constexpr int kStages = 3;
-constexpr int kConsumerWarps = 16;
-constexpr int kConsumers = kConsumerWarps * 32;
-constexpr int kThreads = kConsumers + 32;            // + producer warp
-constexpr uint32_t kStageBytes = 72 * 1024;          // q | k | v token rows of one tile
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 128 + 128;  // + barriers + alignment slack
+constexpr int kMaxStages = 8;
+constexpr int kStagesWanted = 3;             // larger tiles beat more stages: per-tile handshakes cost
+constexpr int kMaxConsumerWarps = 20;
+constexpr int kProducerWarps = 3;            // warp 0 of the group also issues the bulk copies
+constexpr int kMinConsumerWarps = 12;
 constexpr int kMaxTileTokens = 8;
+constexpr int kMultBatch = 4;                // table loads in flight per producer lane
+constexpr uint32_t kSmemLimit = 220 * 1024;  // stages + barriers; the rest stays L1
+constexpr uint32_t kTailBytes = 512;         // barriers, abort flag, alignment slack
 }  // namespace staged
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -169,8 +144,12 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
+// Stage layout: q rows | k rows | v rows (tile_tokens x row_bytes each) | multiplier rows
+// (tile_tokens x half complex doubles).  The producer group (the last warps) issues the bulk copies
+// of a tile and builds the tile's multiplier rows from the rope table; each of its warps then
+// arrives on the stage's "full" barrier, which completes once the copied bytes are in as well.
 template <typename T>
-__global__ void __launch_bounds__(staged::kThreads, 1)
+__global__ void __launch_bounds__((staged::kMaxConsumerWarps + staged::kProducerWarps) * 32, 1)
 rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
   using namespace staged;
   constexpr int kPairs = Vec<T>::kPairs;
@@ -179,16 +158,25 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 127u) & ~127u;
   uint8_t* gbase = smem_raw + (base - raw);
-  const uint32_t bar0 = base + kStages * kStageBytes;  // full[kStages], empty[kStages]
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + kStages * kStageBytes + 64);
+  const int consumer_warps = (blockDim.x >> 5) - kProducerWarps;
+  const int consumers = consumer_warps * 32;
+  const uint32_t row_bytes = static_cast<uint32_t>(p.heads) * p.head_dim * sizeof(T);
+  const int tile_tokens = p.tile_tokens;
+  const uint32_t tensor_stride = tile_tokens * row_bytes;
+  const uint32_t mult_off = 3 * tensor_stride;
+  const uint32_t mult_row_bytes = static_cast<uint32_t>(p.half) * 16u;
+  const uint32_t stage_bytes = p.stage_bytes;
+  const int kStages = p.stages;
+  const uint32_t bar0 = base + kStages * stage_bytes;  // full[stages], empty[stages]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + kStages * stage_bytes + 16 * kMaxStages);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar0 + 8 * s, 1);
-      mbar_init(bar0 + 8 * (kStages + s), kConsumerWarps);
+      mbar_init(bar0 + 8 * s, kProducerWarps);
+      mbar_init(bar0 + 8 * (kStages + s), consumer_warps);
     }
     fence_mbar_init();
     if (blockIdx.x == 0) write_index(p);
@@ -199,12 +187,11 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
   const int64_t total = static_cast<int64_t>(p.rows) * p.tokens;
   const int lo = static_cast<int>(total * blockIdx.x / gridDim.x);
   const int hi = static_cast<int>(total * (blockIdx.x + 1) / gridDim.x);
-  const uint32_t row_bytes = static_cast<uint32_t>(p.heads) * p.head_dim * sizeof(T);
-  const int tile_tokens = p.tile_tokens;
-  const uint32_t tensor_stride = tile_tokens * row_bytes;  // q | k | v blocks inside a stage
 
-  if (warp == kConsumerWarps) {
-    // ---------------------------------------------------------------- producer
+  if (warp >= consumer_warps) {
+    // ---------------------------------------------------------------- producer group
+    const int pw = warp - consumer_warps;                 // 0 issues the copies
+    const int plane_id = pw * 32 + lane;                  // lane inside the group
     int cur = lo, i = 0;
     bool ok = true;
     while (cur < hi && ok) {
@@ -217,20 +204,46 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
-      if (lane == 0) mbar_expect_tx(bar0 + 8 * s, 3u * n * row_bytes);
-      __syncwarp();
-      const uint32_t sbase = base + s * kStageBytes;
-      for (int c = lane; c < 3 * n; c += 32) {
+      const uint32_t sbase = base + s * stage_bytes;
+      for (int c = lane; pw == 0 && c < 3 * n; c += 32) {
         const int which = c / n;  // 0 q, 1 k, 2 v
         const int j = c - which * n;
         const sdv2_view& vw = which == 0 ? p.q : (which == 1 ? p.k : p.v);
         const T* src = static_cast<const T*>(vw.ptr) + b * vw.stride_row + static_cast<int64_t>(t0 + j) * vw.stride_tok;
         bulk_load(sbase + which * tensor_stride + j * row_bytes, src, row_bytes, bar0 + 8 * s);
       }
+      double2* mult = reinterpret_cast<double2*>(gbase + s * stage_bytes + mult_off);
+      const int64_t frame0 = p.start_frame[b];
+      const int n_ent = n * p.half;
+      for (int e0 = plane_id; e0 < n_ent; e0 += kProducerWarps * 32 * kMultBatch) {
+        double2 val[kMultBatch];  // all loads of a batch in flight before the first store
+#pragma unroll
+        for (int u = 0; u < kMultBatch; ++u) {
+          const int e = e0 + kProducerWarps * 32 * u;
+          if (e < n_ent) {
+            const int j = fast_div(e, p.magic_half);
+            const int col = e - j * p.half;
+            const int t = t0 + j;
+            const int f = fast_div(t, p.magic_plane);
+            const int rem = t - f * p.plane;
+            const int y = fast_div(rem, p.magic_w);
+            val[u] = table_entry(p, col, frame0 + f, y, rem - y * p.grid_w);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kMultBatch; ++u)
+          if (e0 + kProducerWarps * 32 * u < n_ent) mult[e0 + kProducerWarps * 32 * u] = val[u];
+      }
+      __syncwarp();
+      // one arrival per producer warp; the phase completes when the copied bytes are in as well
+      if (lane == 0) {
+        if (pw == 0) mbar_expect_tx(bar0 + 8 * s, 3u * n * row_bytes);
+        else mbar_arrive(bar0 + 8 * s);
+      }
       cur += n;
       ++i;
     }
-    if (!ok && lane == 0) {
+    if (!ok && lane == 0 && pw == 0) {
       // leave no copy in flight: bounded wait for the stages already requested
       for (int k = (i > kStages ? i - kStages : 0); k < i; ++k) {
         const long long t0c = clock64();
@@ -251,32 +264,29 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
       bool ok = mbar_wait(bar0 + 8 * s, (i / kStages) & 1, abort_flag, p.status, WAIT_KV_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      const uint8_t* sq = gbase + s * kStageBytes;
+      const uint8_t* sq = gbase + s * stage_bytes;
       const int n_vec = n * row_vecs;
-      for (int v = threadIdx.x; v < n_vec; v += kConsumers) {
+      const int64_t slot0 = p.dst_begin[b] + t0;
+      T* qo_base = static_cast<T*>(p.q_out.ptr) + b * p.q_out.stride_row + t0 * p.q_out.stride_tok;
+      T* kc_base = static_cast<T*>(p.k_cache.ptr) + b * p.k_cache.stride_row + slot0 * p.k_cache.stride_tok;
+      T* vc_base = static_cast<T*>(p.v_cache.ptr) + b * p.v_cache.stride_row + slot0 * p.v_cache.stride_tok;
+      for (int v = threadIdx.x; v < n_vec; v += consumers) {
         const int j = fast_div(v, p.magic_row_vecs);  // token inside the tile
         const int rv = v - j * row_vecs;               // vector inside the token row
         const int h = fast_div(rv, p.magic_vph);
         const int c = rv - h * vph;
-        const int t = t0 + j;
-        const int f = fast_div(t, p.magic_plane);
-        const int rem = t - f * p.plane;
-        const int y = fast_div(rem, p.magic_w);
-        const int x = rem - y * p.grid_w;
+        const double2* mrow = reinterpret_cast<const double2*>(sq + mult_off + j * mult_row_bytes) + c * kPairs;
         double2 cs[kPairs];
-        load_cs<kPairs>(p, c, p.start_frame[b] + f, y, x, cs);
+#pragma unroll
+        for (int q = 0; q < kPairs; ++q) cs[q] = mrow[q];
         const uint32_t off = static_cast<uint32_t>(j) * row_bytes + static_cast<uint32_t>(rv) * 16u;
         const uint4 qv = *reinterpret_cast<const uint4*>(sq + off);
         const uint4 kv = *reinterpret_cast<const uint4*>(sq + tensor_stride + off);
         const uint4 vv = *reinterpret_cast<const uint4*>(sq + 2 * tensor_stride + off);
-        const int64_t slot = p.dst_begin[b] + t;
         const int e0 = c * kElems;
-        T* qo = static_cast<T*>(p.q_out.ptr) + b * p.q_out.stride_row + t * p.q_out.stride_tok + h * p.q_out.stride_head + e0;
-        T* kc = static_cast<T*>(p.k_cache.ptr) + b * p.k_cache.stride_row + slot * p.k_cache.stride_tok + h * p.k_cache.stride_head + e0;
-        T* vc = static_cast<T*>(p.v_cache.ptr) + b * p.v_cache.stride_row + slot * p.v_cache.stride_tok + h * p.v_cache.stride_head + e0;
-        *reinterpret_cast<uint4*>(vc) = vv;
-        *reinterpret_cast<uint4*>(qo) = Vec<T>::rope(qv, cs);
-        *reinterpret_cast<uint4*>(kc) = Vec<T>::rope(kv, cs);
+        *reinterpret_cast<uint4*>(vc_base + j * p.v_cache.stride_tok + h * p.v_cache.stride_head + e0) = vv;
+        *reinterpret_cast<uint4*>(qo_base + j * p.q_out.stride_tok + h * p.q_out.stride_head + e0) = Vec<T>::rope(qv, cs);
+        *reinterpret_cast<uint4*>(kc_base + j * p.k_cache.stride_tok + h * p.k_cache.stride_head + e0) = Vec<T>::rope(kv, cs);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar0 + 8 * (kStages + s));
@@ -288,46 +298,69 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
 
 static uint32_t magic_of(uint32_t d) { return static_cast<uint32_t>(((1ull << 32) + d - 1) / d); }
 
+template <typename T>
+static cudaError_t launch_staged(const AppendParams& p, int grid, int threads, uint32_t smem, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(rope_kv_append_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  rope_kv_append_staged_kernel<T><<<grid, threads, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_rope_kv_append(const AppendParams& p_in, int dtype, cudaStream_t stream) {
   AppendParams p = p_in;
   const int esize = dtype == SDV2_DTYPE_BF16 ? 2 : 4;
   const int elems = 16 / esize;
   const int vph = p.head_dim / elems;
+  const int row_vecs = p.heads * vph;
+  const uint32_t row_bytes = static_cast<uint32_t>(p.heads) * p.head_dim * esize;
   p.plane = p.grid_h * p.grid_w;
   p.magic_plane = magic_of(p.plane);
   p.magic_w = magic_of(p.grid_w);
-  const int row_vecs = p.heads * vph;
   p.magic_row_vecs = magic_of(row_vecs);
   p.magic_vph = magic_of(vph);
-  const uint32_t row_bytes = static_cast<uint32_t>(p.heads) * p.head_dim * esize;
+  p.magic_half = magic_of(p.half);
   // fast_div is exact while numerator * divisor < 2^32
   const bool div_ok = static_cast<uint64_t>(p.tokens) * p.plane < (1ull << 32) &&
                       static_cast<uint64_t>(staged::kMaxTileTokens) * row_vecs * row_vecs < (1ull << 32);
-  if (!div_ok || vph > 256) return cudaErrorInvalidValue;
+  if (!div_ok || vph > 256 || vph < 1) return cudaErrorInvalidValue;
+
   const bool rows_contiguous = p.q.stride_head == p.head_dim && p.k.stride_head == p.head_dim &&
                                p.v.stride_head == p.head_dim;
-  int tile_tokens = static_cast<int>(staged::kStageBytes / (3u * row_bytes));
-  if (tile_tokens > staged::kMaxTileTokens) tile_tokens = staged::kMaxTileTokens;
-  if (rows_contiguous && tile_tokens >= 1) {
-    p.tile_tokens = tile_tokens;
+  // tile size and consumer-warp count: the tile's vectors should split evenly over the consumer
+  // threads and three stages must fit in shared memory; then more warps and larger tiles
+  const uint32_t mult_row = static_cast<uint32_t>(p.half) * 16u;
+  int best_tt = 0, best_w = 0;
+  double best_score = 0.0;
+  for (int tt = 1; tt <= staged::kMaxTileTokens; ++tt) {
+    const uint32_t stage = (3u * tt * row_bytes + tt * mult_row + 127u) & ~127u;
+    if (static_cast<uint64_t>(stage) * staged::kStagesWanted + staged::kTailBytes > staged::kSmemLimit) break;
+    for (int w = staged::kMinConsumerWarps; w <= staged::kMaxConsumerWarps; ++w) {
+      const int n_vec = tt * row_vecs, thr = 32 * w;
+      const int iters = (n_vec + thr - 1) / thr;
+      const double util = static_cast<double>(n_vec) / (static_cast<double>(iters) * thr);
+      const double score = util + 1e-3 * w + 1e-4 * tt;
+      if (score > best_score) {
+        best_score = score;
+        best_tt = tt;
+        best_w = w;
+      }
+    }
+  }
+  if (rows_contiguous && best_tt >= 1) {
+    p.tile_tokens = best_tt;
+    p.stage_bytes = (3u * best_tt * row_bytes + best_tt * mult_row + 127u) & ~127u;
+    p.stages = staged::kStagesWanted;
+    const uint32_t smem = p.stages * p.stage_bytes + staged::kTailBytes;
     int dev = 0, sms = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
     const int64_t total = static_cast<int64_t>(p.rows) * p.tokens;
     const int grid = static_cast<int>(total < sms ? total : sms);
-    if (dtype == SDV2_DTYPE_BF16) {
-      e = cudaFuncSetAttribute(rope_kv_append_staged_kernel<__nv_bfloat16>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(staged::kSmemBytes));
-      if (e != cudaSuccess) return e;
-      rope_kv_append_staged_kernel<__nv_bfloat16><<<grid, staged::kThreads, staged::kSmemBytes, stream>>>(p);
-    } else {
-      e = cudaFuncSetAttribute(rope_kv_append_staged_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(staged::kSmemBytes));
-      if (e != cudaSuccess) return e;
-      rope_kv_append_staged_kernel<float><<<grid, staged::kThreads, staged::kSmemBytes, stream>>>(p);
-    }
-    return cudaGetLastError();
+    const int threads = (best_w + staged::kProducerWarps) * 32;
+    return dtype == SDV2_DTYPE_BF16 ? launch_staged<__nv_bfloat16>(p, grid, threads, smem, stream)
+                                    : launch_staged<float>(p, grid, threads, smem, stream);
   }
   const int tok_per_block = 256 / vph;
   dim3 grid((p.tokens + tok_per_block - 1) / tok_per_block, p.heads, p.rows);

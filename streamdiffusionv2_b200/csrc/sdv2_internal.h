@@ -16,8 +16,10 @@ struct AppendParams {
   int cols_t, cols_h;  // complex columns in the temporal and height groups (width gets the rest)
   // filled in by the launcher
   int plane;                // grid_h * grid_w
-  uint32_t magic_plane, magic_w, magic_row_vecs, magic_vph;  // ceil(2^32 / d) for exact n / d
+  uint32_t magic_plane, magic_w, magic_row_vecs, magic_vph, magic_half;  // ceil(2^32 / d) for exact n / d
   int tile_tokens;          // tokens per shared-memory stage (staged kernel)
+  uint32_t stage_bytes;     // bytes of one stage: q | k | v rows | multiplier rows
+  int stages;               // stages in the shared-memory ring
   int* status;              // optional device word that records an abandoned wait
   int64_t* global_end_dev;
   int64_t* local_end_dev;
