@@ -1,0 +1,86 @@
+"""Per-rank driver of the pipeline-parallel stream: one rank per GPU, contiguous block ranges,
+activations handed from stage to stage by `StageLink`.
+
+Mirrors the data flow of the reference's rank loops (streamv2v/inference_pipe.py:511-800):
+
+* stage 0 shifts the new chunk into the stage batch, runs its blocks and sends activations plus
+  the stage-batch latents and row starts/ends downstream; once the ring is full it first adopts
+  the latents and row indices that came back from the last stage `world_size` chunks earlier;
+* middle stages receive, run their blocks on the received activations, forward;
+* the last stage runs the remaining blocks, the head, the x0 conversion and the re-noising, and
+  returns the new stage-batch latents to stage 0 (latents only; the reference also ships the
+  activations back, which nobody reads).
+
+`world_size` chunks are in flight around the ring, one per stage.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from .stage_transport import StageLink, StagePacket, contiguous_block_ranges
+from .stream_pipeline import StreamPipeline
+
+
+class PipelineStageRunner:
+    def __init__(self, pipe: StreamPipeline, link: StageLink, rank: int, world_size: int,
+                 block_ranges: Optional[Sequence[Sequence[int]]] = None):
+        self.pipe, self.link, self.rank, self.world = pipe, link, rank, world_size
+        ranges = block_ranges or contiguous_block_ranges(pipe.num_transformer_blocks, world_size)
+        self.block_range = [int(ranges[rank][0]), int(ranges[rank][1])]
+        self.role = "input" if rank == 0 else ("output" if rank == world_size - 1 else "middle")
+        self.items = 0
+        self._posted_first = False
+
+    @property
+    def owned_blocks(self) -> range:
+        return range(self.block_range[0], self.block_range[1])
+
+    # ------------------------------------------------------------------ one chunk on this rank
+    def step(self, chunk_idx: int = 0, noise: Optional[torch.Tensor] = None, current_start: Optional[int] = None,
+             current_end: Optional[int] = None, current_step: Optional[int] = None) -> Optional[torch.Tensor]:
+        """Process one chunk on this rank.  Stage 0 needs `noise`, `current_start`, `current_end`
+        (and optionally the adaptive `current_step`); the other stages take everything from the
+        packet they receive.  The last stage returns the denoised stage batch, the others None."""
+        pipe, link = self.pipe, self.link
+        if self.role == "input":
+            if self.items >= self.world:
+                back = link.recv()                      # what the last stage made of chunk items-world
+                link.post_recv()
+                pipe.hidden_states.copy_(back.latents)
+                pipe.kv_cache_starts.copy_(torch.tensor(back.starts, dtype=torch.long), non_blocking=True)
+                pipe.kv_cache_ends.copy_(torch.tensor(back.ends, dtype=torch.long), non_blocking=True)
+                pipe._starts_host = list(back.starts)
+                pipe._ends_host = list(back.ends)
+            elif self.items == self.world - 1:
+                link.post_recv()
+            act, _ = pipe.inference(noise=noise, current_start=current_start, current_end=current_end,
+                                    current_step=current_step, block_mode="input", block_num=self.block_range)
+            link.send(chunk_idx, act, pipe.hidden_states, pipe.generator.model.last_patched_x_shape,
+                      pipe._starts_host, pipe._ends_host, -1 if current_step is None else int(current_step))
+            self.items += 1
+            return None
+
+        pkt: StagePacket = link.recv()
+        link.post_recv()
+        step = None if pkt.current_step < 0 else pkt.current_step
+        out, pshape = pipe.inference(noise=pkt.latents, current_start=pkt.starts, current_end=pkt.ends,
+                                     current_step=step, block_mode=self.role, block_num=self.block_range,
+                                     patched_x_shape=pkt.patched_x_shape, block_x=pkt.activations,
+                                     starts_host=pkt.starts)
+        if self.role == "middle":
+            link.send(pkt.chunk_idx, out, pkt.latents, pkt.patched_x_shape, pkt.starts, pkt.ends, pkt.current_step)
+            self.items += 1
+            return None
+        link.send(pkt.chunk_idx, None, out, pkt.patched_x_shape, pkt.starts, pkt.ends, pkt.current_step)
+        self.items += 1
+        return out
+
+    def finish(self) -> None:
+        """Stage 0 takes in the packets still travelling back to it; everyone waits for its sends."""
+        if self.role == "input":
+            # the last stage returns one packet per chunk; items - world of them were taken in
+            for _ in range(self.items - max(self.items - self.world, 0)):
+                self.link.recv()
+        self.link.drain()

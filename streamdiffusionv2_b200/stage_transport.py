@@ -1,0 +1,181 @@
+"""Ring hand-off between pipeline-parallel stages of the DiT.
+
+Replaces the reference's per-hop protocol (streamv2v/communication/distributed_communicator.py
+:158-264: two shape headers, two payloads and two index vectors per hop, each header read back
+to the host before its payload can be received) with
+
+* one fixed-shape device payload per hop: stage activations [rows, tokens, dim] and the
+  stage-batch latents [rows, frames, C, H, W] packed in one bf16 buffer, moved by a single
+  NCCL point-to-point operation on the edge's own communicator (stages talk over NVLink);
+* one small host-side metadata message (chunk index, denoise step of row 0, patched shape,
+  per-row chunk starts/ends) on a CPU (gloo) group, so the receiver knows every integer it
+  needs without reading device memory back.
+
+Every ring edge r -> r+1 has its own two-rank process group, hence its own communicator and
+stream: receiving chunk c+1 overlaps computing chunk c and sending chunk c-1.  Receive buffers
+are double-buffered; a receive is posted before the compute of the previous chunk is enqueued.
+The closing edge (last stage -> stage 0) carries latents only.
+
+`chunk_idx == -1` is kept as the restart sentinel of the reference drivers
+(streamv2v/inference_pipe.py:459-472).
+
+Works on CPU tensors with the gloo backend too, which is how the host logic is tested.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass
+from typing import Deque, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class StagePacket:
+    chunk_idx: int
+    current_step: int
+    patched_x_shape: List[int]
+    starts: List[int]
+    ends: List[int]
+    activations: Optional[torch.Tensor]   # [rows, tokens, dim]; None on the closing edge
+    latents: torch.Tensor                 # [rows, frames, C, H, W]
+
+
+def contiguous_block_ranges(total_blocks: int, world_size: int) -> List[List[int]]:
+    """Contiguous [start, end) block ranges per stage, as the reference driver splits them
+    (streamv2v/inference_pipe.py:59-74): halves for two stages, otherwise the remainder goes to
+    the first stages."""
+    if world_size == 2:
+        mid = total_blocks // 2
+        return [[0, mid], [mid, total_blocks]]
+    base, rem = divmod(total_blocks, world_size)
+    out, start = [], 0
+    for r in range(world_size):
+        end = start + base + (1 if r < rem else 0)
+        if r == world_size - 1:
+            end = total_blocks
+        out.append([start, end])
+        start = end
+    return out
+
+
+class _Edge:
+    """One direction of one ring edge as seen from this rank."""
+
+    def __init__(self, group, meta_group, peer: int, numel: int, meta_len: int, dtype, device, depth: int = 2):
+        self.group, self.meta_group, self.peer = group, meta_group, peer
+        self.bufs = [torch.empty(numel, dtype=dtype, device=device) for _ in range(depth)]
+        self.meta = [torch.zeros(meta_len, dtype=torch.int64) for _ in range(depth)]
+        self.works: List[Optional[object]] = [None] * depth
+        self.meta_works: List[Optional[object]] = [None] * depth
+        self.next = 0
+        self.posted: Deque[int] = deque()
+
+
+class StageLink:
+    """Point-to-point links of one stage: `up` (from the previous stage) and `down` (to the next)."""
+
+    META_FIXED = 7  # chunk_idx, current_step, patched_x_shape[5]
+
+    def __init__(self, rank: int, world_size: int, device: torch.device, act_shape: Sequence[int],
+                 latent_shape: Sequence[int], dtype=torch.bfloat16, timeout_s: float = 120.0):
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        if world_size < 2:
+            raise ValueError("a pipeline needs at least two stages")
+        self.rank, self.world, self.device = rank, world_size, torch.device(device)
+        self.act_shape, self.latent_shape = tuple(act_shape), tuple(latent_shape)
+        self.rows = self.latent_shape[0]
+        self.act_numel = int(torch.Size(self.act_shape).numel())
+        self.lat_numel = int(torch.Size(self.latent_shape).numel())
+        self.meta_len = self.META_FIXED + 2 * self.rows
+        import datetime
+        to = datetime.timedelta(seconds=timeout_s)
+        # every rank creates every group, in the same order
+        self._edge_groups = [dist.new_group([i, (i + 1) % world_size], timeout=to) for i in range(world_size)]
+        self._meta_groups = [dist.new_group([i, (i + 1) % world_size], backend="gloo", timeout=to)
+                             for i in range(world_size)]
+        prev_rank, next_rank = (rank - 1) % world_size, (rank + 1) % world_size
+        up_edge, down_edge = prev_rank, rank          # edge i connects i -> i+1
+        closing_up = rank == 0                         # stage 0 receives the closing edge
+        closing_down = rank == world_size - 1
+        self.up = _Edge(self._edge_groups[up_edge], self._meta_groups[up_edge], prev_rank,
+                        self.lat_numel + (0 if closing_up else self.act_numel), self.meta_len, dtype, self.device)
+        self.down = _Edge(self._edge_groups[down_edge], self._meta_groups[down_edge], next_rank,
+                          self.lat_numel + (0 if closing_down else self.act_numel), self.meta_len, dtype,
+                          self.device)
+        self._up_has_act, self._down_has_act = not closing_up, not closing_down
+        self._side = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+
+    # ------------------------------------------------------------------ receive side
+    def post_recv(self) -> None:
+        """Post the receive of the next packet from the previous stage.  Call it right after
+        `recv()` returned and before enqueuing the compute that consumes that packet, so that the
+        transfer only waits for work that is already ahead of it."""
+        e = self.up
+        i = e.next
+        e.next = (i + 1) % len(e.bufs)
+        if self._side is not None:
+            # order after everything already enqueued on the compute stream (the previous user of
+            # this buffer), but not after what the caller enqueues next
+            self._side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self._side):
+                e.works[i] = dist.irecv(e.bufs[i], src=e.peer, group=e.group)
+        else:
+            e.works[i] = dist.irecv(e.bufs[i], src=e.peer, group=e.group)
+        e.meta_works[i] = dist.irecv(e.meta[i], src=e.peer, group=e.meta_group)
+        e.posted.append(i)
+
+    def recv(self) -> StagePacket:
+        """Next packet from the previous stage.  Blocks the host only for the metadata message;
+        the payload is ordered on the current CUDA stream."""
+        e = self.up
+        if not e.posted:
+            self.post_recv()
+        i = e.posted.popleft()
+        e.meta_works[i].wait()
+        e.works[i].wait()          # NCCL: makes the current stream wait; gloo: blocks
+        m = e.meta[i].tolist()
+        buf = e.bufs[i]
+        act = buf[:self.act_numel].view(self.act_shape) if self._up_has_act else None
+        lat = buf[(self.act_numel if self._up_has_act else 0):].view(self.latent_shape)
+        r = self.rows
+        return StagePacket(int(m[0]), int(m[1]), [int(x) for x in m[2:7]], [int(x) for x in m[7:7 + r]],
+                           [int(x) for x in m[7 + r:7 + 2 * r]], act, lat)
+
+    # ------------------------------------------------------------------ send side
+    def send(self, chunk_idx: int, activations: Optional[torch.Tensor], latents: torch.Tensor,
+             patched_x_shape: Sequence[int], starts: Sequence[int], ends: Sequence[int], current_step: int) -> None:
+        """Hand a packet to the next stage; returns immediately (the copy into the send buffer and
+        the transfer are ordered after the work already enqueued on the current stream)."""
+        e = self.down
+        i = e.next
+        e.next = (i + 1) % len(e.bufs)
+        if e.works[i] is not None:
+            e.works[i].wait()          # the transfer that last used this buffer
+            e.meta_works[i].wait()
+        buf = e.bufs[i]
+        off = 0
+        if self._down_has_act:
+            if activations is None or activations.numel() != self.act_numel:
+                raise ValueError("activations do not match the link's fixed shape")
+            buf[:self.act_numel].view(self.act_shape).copy_(activations)
+            off = self.act_numel
+        if latents.numel() != self.lat_numel:
+            raise ValueError("latents do not match the link's fixed shape")
+        buf[off:].view(self.latent_shape).copy_(latents)
+        if len(starts) != self.rows or len(ends) != self.rows or len(patched_x_shape) != 5:
+            raise ValueError("metadata does not match the link's row count")
+        e.meta[i].copy_(torch.tensor([chunk_idx, current_step, *patched_x_shape, *starts, *ends], dtype=torch.int64))
+        e.meta_works[i] = dist.isend(e.meta[i], dst=e.peer, group=e.meta_group)
+        e.works[i] = dist.isend(buf, dst=e.peer, group=e.group)
+
+    def drain(self) -> None:
+        """Wait for every outstanding send (call before tearing the process group down)."""
+        for e in (self.down,):
+            for w in list(e.works) + list(e.meta_works):
+                if w is not None:
+                    w.wait()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)

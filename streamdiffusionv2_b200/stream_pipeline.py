@@ -133,6 +133,7 @@ class StreamPipeline(nn.Module):
         self.block_x = None
         self.conditional_dict = None
         self._starts_host: List[int] = []
+        self._ends_host: List[int] = []
 
     # ------------------------------------------------------------------ cache allocation
     def _initialize_kv_cache(self, batch_size, dtype, device):
@@ -159,10 +160,13 @@ class StreamPipeline(nn.Module):
 
     # ------------------------------------------------------------------ first chunk
     def prepare(self, text_prompts, device, dtype, block_mode="input", noise=None, current_start=0,
-                current_end=None, block_num=None, batch_denoise=True, owned_blocks: Optional[range] = None):
+                current_end=None, block_num=None, batch_denoise=True, owned_blocks: Optional[range] = None,
+                unowned: str = "cpu"):
         """Runs the first chunk through every denoise level with one cache row, then replicates the
         caches to one row per level (causal_stream_inference.py:124-255).  `owned_blocks`, when
-        given, keeps only that range of K/V caches on the device (pipeline-parallel stage)."""
+        given, keeps only that range of K/V caches on the device (pipeline-parallel stage); the
+        others are moved to host memory as the reference does (`unowned="cpu"`) or released
+        (`unowned="free"`)."""
         self.device = torch.device(device)
         batch_size = noise.shape[0]
         self.conditional_dict = self.text_encoder(text_prompts=text_prompts)
@@ -200,13 +204,15 @@ class StreamPipeline(nn.Module):
             if torch.distributed.is_available() and torch.distributed.is_initialized():
                 for t in (cc["k"], cc["v"], kv["k"], kv["v"]):
                     torch.distributed.broadcast(t, src=0)
+            if owned_blocks is not None and i not in owned_blocks and unowned == "free":
+                kv["k"], kv["v"] = kv["k"][:, :0], kv["v"][:, :0]
             kv["k"] = kv["k"].repeat(levels, 1, 1, 1)
             kv["v"] = kv["v"].repeat(levels, 1, 1, 1)
             kv["global_end_index"] = kv["global_end_index"].repeat(levels)
             kv["local_end_index"] = kv["local_end_index"].repeat(levels)
             cc["k"] = cc["k"].expand(levels, -1, -1, -1)
             cc["v"] = cc["v"].expand(levels, -1, -1, -1)
-            if owned_blocks is not None and i not in owned_blocks:
+            if owned_blocks is not None and i not in owned_blocks and unowned == "cpu":
                 kv["k"], kv["v"] = kv["k"].cpu(), kv["v"].cpu()
 
         self.hidden_states = torch.zeros((levels, self.num_frame_per_block, *noise.shape[2:]), dtype=noise.dtype,
@@ -221,6 +227,7 @@ class StreamPipeline(nn.Module):
         self.kv_cache_starts = torch.ones(levels, dtype=torch.long, device=device) * current_end
         self.kv_cache_ends = torch.ones(levels, dtype=torch.long, device=device) * current_end + self.frame_seq_length
         self._starts_host = [int(current_end)] * levels
+        self._ends_host = [int(current_end) + self.frame_seq_length] * levels
         self.timestep = self.denoising_step_list
         self.conditional_dict["prompt_embeds"] = self.conditional_dict["prompt_embeds"].repeat(levels, 1, 1)
         return denoised
@@ -234,6 +241,7 @@ class StreamPipeline(nn.Module):
         self.kv_cache_ends[1:] = self.kv_cache_ends[:-1].clone()
         self.kv_cache_ends[0] = current_end
         self._starts_host = [int(current_start)] + self._starts_host[:-1]
+        self._ends_host = [int(current_end)] + self._ends_host[:-1]
 
     def _renoise(self, x):
         for i in range(len(self.denoising_step_list) - 1):
@@ -289,8 +297,16 @@ class StreamPipeline(nn.Module):
         else:
             self.block_x.copy_(block_x)
             self.hidden_states.copy_(noise)
-            self.kv_cache_starts.copy_(current_start)
-            self.kv_cache_ends.copy_(current_end)
+            if not isinstance(current_start, torch.Tensor):   # host lists: no read-back needed
+                starts_host = current_start
+                current_start = torch.tensor(list(current_start), dtype=torch.long)
+            if not isinstance(current_end, torch.Tensor):
+                self._ends_host = [int(v) for v in current_end]
+                current_end = torch.tensor(list(current_end), dtype=torch.long)
+            else:
+                self._ends_host = [int(v) for v in current_end.tolist()]
+            self.kv_cache_starts.copy_(current_start, non_blocking=True)
+            self.kv_cache_ends.copy_(current_end, non_blocking=True)
             self._starts_host = [int(v) for v in (starts_host if starts_host is not None else current_start.tolist())]
         if current_step is not None:
             self.timestep[0] = current_step

@@ -178,6 +178,7 @@ class CausalWanModel(nn.Module):
         # plain attribute, not a buffer: .to(dtype) must not touch it (causal_model.py:630-638)
         self.freqs = build_rope_table(head_dim)
         self.num_frame_per_block = 1
+        self.last_patched_x_shape = None
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -217,7 +218,8 @@ class CausalWanModel(nn.Module):
         if block_mode == "input":
             x = self.patch_embedding(x if isinstance(x, torch.Tensor) else torch.stack(list(x)))
             bsz, cch, frames, gh, gw = x.shape
-            patched_x_shape = torch.tensor([1, cch, frames, gh, gw], dtype=torch.int64, device=device)
+            self.last_patched_x_shape = [1, int(cch), int(frames), int(gh), int(gw)]   # host copy for stage links
+            patched_x_shape = torch.tensor(self.last_patched_x_shape, dtype=torch.int64, device=device)
             x = x.flatten(2).transpose(1, 2)
         else:
             _, cch, frames, gh, gw = _as_ints(patched_x_shape)

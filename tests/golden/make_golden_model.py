@@ -89,21 +89,29 @@ def run_stages(ref, case):
             pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
                          current_start=0, current_end=fs * (1 + case["frames"]), block_mode=mode)
         torch.manual_seed(case["seed"] + 2)
-        noise_in = None
+        world = 2
+        returns = []     # what the last stage sent back for every chunk: (latents, starts, ends)
         for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
-            # the last stage's re-noised rows come back to the first stage on the next chunk
-            if noise_in is not None:
-                pa.hidden_states.copy_(noise_in)
+            # stage 0 adopts the packet that came back from chunk i - world before running chunk i
+            # (streamv2v/inference_pipe.py:583-634: receive once `processed >= world_size`, copy into
+            # the pipeline state after the send)
+            if i >= world:
+                lat, st, en = returns[i - world]
+                pa.hidden_states.copy_(lat)
+                pa.kv_cache_starts.copy_(st)
+                pa.kv_cache_ends.copy_(en)
             act, pshape = pa.inference(noise=noise, current_start=cs, current_end=ce, current_step=None,
                                        block_mode="input", block_num=torch.tensor([0, split]))
-            den, _ = pb.inference(noise=pa.hidden_states, current_start=pa.kv_cache_starts,
-                                  current_end=pa.kv_cache_ends, current_step=None, block_mode="output",
+            sent_starts, sent_ends = pa.kv_cache_starts.clone(), pa.kv_cache_ends.clone()
+            den, _ = pb.inference(noise=pa.hidden_states.clone(), current_start=sent_starts,
+                                  current_end=sent_ends, current_step=None, block_mode="output",
                                   block_num=torch.tensor([split, nblk]), patched_x_shape=pshape, block_x=act)
-            noise_in = den.clone()
+            returns.append((den.clone(), sent_starts, sent_ends))
             arrays[f"act_{i}"] = act.numpy().copy()
             arrays[f"out_{i}"] = den.numpy().copy()
             meta["steps"].append({"stageA_layer0": snapshot(pa, 0), "stageB_layerL": snapshot(pb, nblk - 1),
-                                  "pshape": pshape.tolist()})
+                                  "pshape": pshape.tolist(), "starts": sent_starts.tolist(),
+                                  "ends": sent_ends.tolist()})
     return meta, arrays
 
 

@@ -55,16 +55,22 @@ def test_two_stage_pipeline_matches_reference(monkeypatch):
             pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
                          current_start=0, current_end=fs * (1 + case["frames"]), block_mode=mode)
         torch.manual_seed(case["seed"] + 2)
-        back = None
+        world, returns = 2, []
         for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
-            if back is not None:
-                pa.hidden_states.copy_(back)
+            if i >= world:                      # ring depth: the return of chunk i-2 arrives now
+                lat, st, en = returns[i - world]
+                pa.hidden_states.copy_(lat)
+                pa.kv_cache_starts.copy_(torch.tensor(st))
+                pa.kv_cache_ends.copy_(torch.tensor(en))
+                pa._starts_host, pa._ends_host = list(st), list(en)
             act, pshape = pa.inference(noise=noise, current_start=cs, current_end=ce, current_step=None,
                                        block_mode="input", block_num=[0, split])
-            den, _ = pb.inference(noise=pa.hidden_states, current_start=pa.kv_cache_starts,
-                                  current_end=pa.kv_cache_ends, current_step=None, block_mode="output",
-                                  block_num=[split, nblk], patched_x_shape=pshape, block_x=act)
-            back = den.clone()
+            st, en = list(pa._starts_host), list(pa._ends_host)
+            assert st == meta["steps"][i]["starts"] and en == meta["steps"][i]["ends"]
+            den, _ = pb.inference(noise=pa.hidden_states.clone(), current_start=st, current_end=en,
+                                  current_step=None, block_mode="output", block_num=[split, nblk],
+                                  patched_x_shape=pshape, block_x=act)
+            returns.append((den.clone(), st, en))
             assert pshape.tolist() == meta["steps"][i]["pshape"]
             assert np.abs(act.numpy() - z[f"act_{i}"]).max() < 5e-4, i
             assert np.abs(den.numpy() - z[f"out_{i}"]).max() < 5e-4, i

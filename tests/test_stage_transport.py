@@ -1,0 +1,207 @@
+"""Pipeline-parallel hand-off on CPU ranks (gloo): the ring transport and the per-rank runner
+reproduce the two-stage fixture recorded from the reference, and survive failures injected on the
+host (a peer that never sends; a packet of the wrong shape)."""
+import os
+import socket
+import sys
+import traceback
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import cases
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _init(rank, world, port):
+    for p in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "tests", "golden")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+
+class _Patch:
+    """Minimal stand-in for pytest's monkeypatch inside a child process."""
+
+    def setattr(self, obj, name, value):
+        setattr(obj, name, value)
+
+
+def _worker_pipeline(rank, world, port, ranges, q):
+    try:
+        _init(rank, world, port)
+        import fake_ops
+        from model_harness import build_pipeline, snapshot
+        from streamdiffusionv2_b200.pipeline_runner import PipelineStageRunner
+        from streamdiffusionv2_b200.stage_transport import StageLink
+        fake_ops.install(_Patch())
+        case = cases.MODEL_CASES["m_stages"]
+        fs, sched = cases.model_schedule(case)
+        pipe, first, chunks = build_pipeline(case)
+        role = "input" if rank == 0 else ("output" if rank == world - 1 else "middle")
+        with torch.no_grad():
+            torch.manual_seed(case["seed"] + 1)
+            pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
+                         current_start=0, current_end=fs * (1 + case["frames"]), block_mode=role)
+            torch.manual_seed(case["seed"] + 2)
+            rows = len(case["levels"])
+            link = StageLink(rank, world, torch.device("cpu"), (rows, fs * case["frames"], cases.MODEL_KW["dim"]),
+                             tuple(pipe.hidden_states.shape), dtype=torch.float32, timeout_s=60)
+            runner = PipelineStageRunner(pipe, link, rank, world, ranges)
+            outs, states = [], []
+            for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
+                o = runner.step(i, noise, cs, ce, None)
+                if o is not None:
+                    outs.append(o.clone().numpy())
+                states.append(snapshot(pipe, runner.block_range[0] if rank == 0 else runner.block_range[1] - 1))
+            runner.finish()
+        q.put((rank, "ok", outs, states))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc(), None))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _run(target, world, *args, timeout=240):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, *args, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    try:
+        for _ in range(world):
+            r = q.get(timeout=timeout)
+            results[r[0]] = r[1:]
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    return results
+
+
+def test_two_rank_pipeline_matches_reference_fixture():
+    case = cases.MODEL_CASES["m_stages"]
+    meta, z = cases.load_fixture("m_stages")
+    nblk, split = cases.MODEL_KW["num_layers"], case["split"]
+    res = _run(_worker_pipeline, 2, [[0, split], [split, nblk]])
+    for r, v in res.items():
+        assert v[0] == "ok", v[1]
+    outs = res[1][1]
+    assert len(outs) == case["chunks"]
+    for i, o in enumerate(outs):
+        assert np.abs(o - z[f"out_{i}"]).max() < 5e-4, i
+    for i in range(case["chunks"]):
+        for key in ("global_end", "local_end", "evict_idx", "current_step"):
+            assert res[0][2][i][key] == meta["steps"][i]["stageA_layer0"][key]
+            assert res[1][2][i][key] == meta["steps"][i]["stageB_layerL"][key]
+
+
+def test_three_rank_pipeline_runs_with_a_middle_stage():
+    """input -> middle -> output over three ranks; index state must stay consistent on every stage
+    (all stages see the same row starts) and the stream must complete."""
+    res = _run(_worker_pipeline, 3, [[0, 1], [1, 2], [2, 3]])
+    for r, v in res.items():
+        assert v[0] == "ok", v[1]
+    n = cases.MODEL_CASES["m_stages"]["chunks"]
+    assert len(res[2][1]) == n
+    for i in range(n):
+        assert res[0][2][i]["global_end"] == res[1][2][i]["global_end"] == res[2][2][i]["global_end"]
+        assert np.isfinite(res[2][1][i]).all()
+
+
+def _worker_fault(rank, world, port, mode, q):
+    try:
+        _init(rank, world, port)
+        from streamdiffusionv2_b200.stage_transport import StageLink
+        link = StageLink(rank, world, torch.device("cpu"), (2, 4, 8), (2, 1, 4, 2, 2), dtype=torch.float32,
+                         timeout_s=3)
+        if mode == "silent_peer":
+            if rank == 1:
+                try:
+                    link.recv()                       # rank 0 never sends
+                    q.put((rank, "no error", None, None))
+                except Exception as e:                # the bounded wait surfaces as an exception
+                    q.put((rank, "raised", type(e).__name__, None))
+            else:
+                import time
+                time.sleep(6)
+                q.put((rank, "idle", None, None))
+        elif mode == "bad_shape":
+            if rank == 0:
+                try:
+                    link.send(0, torch.zeros(2, 4, 9), torch.zeros(2, 1, 4, 2, 2), [1, 8, 1, 2, 2], [0, 0], [4, 4], 0)
+                    q.put((rank, "no error", None, None))
+                except ValueError:
+                    q.put((rank, "raised", "ValueError", None))
+            else:
+                q.put((rank, "idle", None, None))
+        elif mode == "roundtrip":
+            if rank == 0:
+                link.send(7, torch.arange(64.).view(2, 4, 8), torch.ones(2, 1, 4, 2, 2), [1, 8, 1, 2, 2], [6, 12],
+                          [12, 18], 500)
+                back = link.recv()
+                q.put((rank, "ok", (back.chunk_idx, back.starts, float(back.latents.sum())), None))
+            else:
+                pkt = link.recv()
+                ok = (pkt.chunk_idx == 7 and pkt.current_step == 500 and pkt.starts == [6, 12]
+                      and pkt.ends == [12, 18] and pkt.patched_x_shape == [1, 8, 1, 2, 2]
+                      and torch.equal(pkt.activations, torch.arange(64.).view(2, 4, 8)))
+                link.send(pkt.chunk_idx, None, pkt.latents * 2, pkt.patched_x_shape, pkt.starts, pkt.ends,
+                          pkt.current_step)
+                q.put((rank, "ok" if ok else "mismatch", None, None))
+            link.drain()
+    except Exception:
+        q.put((rank, "error", traceback.format_exc(), None))
+    finally:
+        try:
+            if dist.is_initialized():
+                dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_packet_roundtrip_two_ranks():
+    res = _run(_worker_fault, 2, "roundtrip", timeout=60)
+    assert res[1][0] == "ok", res[1]
+    assert res[0][0] == "ok" and res[0][1] == (7, [6, 12], 64.0), res[0]
+
+
+def test_silent_peer_times_out_instead_of_hanging():
+    """Failure made on the host: the upstream rank never sends.  The receiver's wait is bounded by
+    the link timeout and raises; nothing spins forever."""
+    res = _run(_worker_fault, 2, "silent_peer", timeout=60)
+    assert res[1][0] == "raised", res[1]
+
+
+def test_wrong_shape_is_rejected_before_anything_is_sent():
+    res = _run(_worker_fault, 2, "bad_shape", timeout=60)
+    assert res[0][0] == "raised", res[0]
+
+
+def test_block_ranges_follow_the_reference_split():
+    from streamdiffusionv2_b200.stage_transport import contiguous_block_ranges as r
+    assert r(30, 2) == [[0, 15], [15, 30]]
+    assert [b - a for a, b in r(30, 4)] == [8, 8, 7, 7]
+    assert [b - a for a, b in r(30, 8)] == [4, 4, 4, 4, 4, 4, 3, 3]
+    assert [b - a for a, b in r(40, 8)] == [5] * 8
+    for n, w in ((30, 4), (30, 8), (40, 4), (7, 3)):
+        rr = r(n, w)
+        assert rr[0][0] == 0 and rr[-1][1] == n and all(rr[i][1] == rr[i + 1][0] for i in range(w - 1))
