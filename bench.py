@@ -307,6 +307,127 @@ def run_single_gpu(args):
     print(json.dumps(line))
 
 
+def run_pipeline(args):
+    """N ranks = N pipeline stages over contiguous block ranges; every rank runs K chunk steps of
+    its own stage, timed on the device between barriers; the slowest rank's time counts."""
+    import torch.distributed as dist
+    from streamdiffusionv2_b200 import ops
+    from streamdiffusionv2_b200.pipeline_runner import PipelineStageRunner
+    from streamdiffusionv2_b200.stage_transport import StageLink, contiguous_block_ranges
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", device_id=device)
+    peaks = measured_peaks()
+    pipe = build_pipeline(device)
+    ranges = contiguous_block_ranges(MODEL_1P3B["num_layers"], world)
+    role = "input" if rank == 0 else ("output" if rank == world - 1 else "middle")
+    g = torch.Generator(device="cpu").manual_seed(2)
+    h, w = LATENT_HW
+    first = torch.randn(1, 1 + FRAMES_PER_CHUNK, 16, h, w, generator=g).to(device=device, dtype=torch.bfloat16)
+    n_host = 8
+    host_chunks = [torch.randn(1, FRAMES_PER_CHUNK, 16, h, w, generator=g).to(torch.bfloat16).pin_memory()
+                   for _ in range(n_host)]
+    dev_chunks = [c.to(device) for c in host_chunks]
+    host_out = torch.empty(FRAMES_PER_CHUNK, 16, h, w, dtype=torch.bfloat16).pin_memory()
+    sched = ChunkSchedule()
+    rows = len(LEVELS)
+    n_tok = FRAMES_PER_CHUNK * FRAME_TOKENS
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        pipe.prepare(text_prompts=["synthetic"], device=device, dtype=torch.bfloat16, noise=first, current_start=0,
+                     current_end=FRAME_TOKENS * (1 + FRAMES_PER_CHUNK), block_mode=role,
+                     owned_blocks=range(ranges[rank][0], ranges[rank][1]), unowned="free")
+        link = StageLink(rank, world, device, (rows, n_tok, MODEL_1P3B["dim"]),
+                         (rows, FRAMES_PER_CHUNK, 16, h, w), dtype=torch.bfloat16, timeout_s=90)
+        runner = PipelineStageRunner(pipe, link, rank, world, ranges)
+        chunk = [0]
+
+        def one_step(src, last=False):
+            cs, ce = sched.next()
+            i = chunk[0]
+            chunk[0] += 1
+            x = src(i) if rank == 0 else None
+            return runner.step(i, x, cs, ce, None, last=last)
+
+        def phase(n, src, sink=None):
+            """n chunk steps, then empty the ring so that the barrier / device synchronise that
+            follows cannot wait on a transfer whose peer is itself waiting at the barrier."""
+            for j in range(n):
+                out = one_step(src, last=(j == n - 1))
+                if sink is not None and out is not None:
+                    sink(out)
+            runner.quiesce()
+
+        resident = lambda i: dev_chunks[i % n_host]
+        phase(12 + world, resident)                       # fill the ring caches until they wrap
+        phase(max(args.warmup, 1), resident)
+        barrier()
+        ops.read_status(device)
+
+        log = ops.LaunchLog(timed=True)
+        ops.set_launch_log(log)
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        phase(args.steps, resident)                       # ring starts empty and ends empty
+        e1.record()
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+        ops.set_launch_log(None)
+        ms = e0.elapsed_time(e1)
+
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e2.record()
+        phase(args.steps, lambda i: host_chunks[i % n_host].to(device, non_blocking=True),
+              sink=lambda out: host_out.copy_(out[-1], non_blocking=True))
+        e3.record()
+        barrier()
+        ms_e2e = e2.elapsed_time(e3)
+        ops.read_status(device)
+
+    att = log.durations_ms("attn_kvcache")
+    stats = torch.tensor([ms, ms_e2e, float(sum(log.counts.values())), statistics.mean(att) if att else 0.0],
+                         dtype=torch.float64, device=device)
+    mx = stats.clone()
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    sm = stats.clone()
+    dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        ms_max, ms_e2e_max = mx[0].item(), mx[1].item()
+        att_ms = sm[3].item() / world
+        att_flops = log.work["attn_kvcache"] / log.counts["attn_kvcache"]
+        achieved = att_flops / (att_ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"]
+        line = {
+            "metric": "streaming_fps_480x832_wan1.3b", "value": VIDEO_FRAMES_PER_CHUNK * args.steps / (ms_max / 1e3),
+            "unit": "video frames/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": VIDEO_FRAMES_PER_CHUNK * args.steps / (ms_e2e_max / 1e3), "unit": "video frames/s",
+                    "ms_per_step": ms_e2e_max / args.steps, "h2d_bytes_per_step": host_chunks[0].numel() * 2,
+                    "d2h_bytes_per_step": host_out.numel() * 2},
+            "gpu_launches": int(sm[2].item()),
+            "roofline": {"kernel": "attn_kvcache (tcgen05)", "bound": "tensor", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
+                         "traffic": None, "avg_launch_ms": att_ms, "flops_per_launch": att_flops},
+            "cpu_baseline": None, "clocks": clocks,
+            "stage_blocks": ranges, "stage_hop_bytes": rows * n_tok * MODEL_1P3B["dim"] * 2,
+        }
+        print(json.dumps(line))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -320,8 +441,7 @@ def main():
         return run_reference_arm(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return run_single_gpu(args)
-    from streamdiffusionv2_b200 import pipeline_bench
-    return pipeline_bench.run(args, sys.modules[__name__])
+    return run_pipeline(args)
 
 
 if __name__ == "__main__":

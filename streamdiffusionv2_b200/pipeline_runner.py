@@ -15,6 +15,7 @@ Mirrors the data flow of the reference's rank loops (streamv2v/inference_pipe.py
 """
 from __future__ import annotations
 
+from collections import deque
 from typing import List, Optional, Sequence
 
 import torch
@@ -30,8 +31,9 @@ class PipelineStageRunner:
         ranges = block_ranges or contiguous_block_ranges(pipe.num_transformer_blocks, world_size)
         self.block_range = [int(ranges[rank][0]), int(ranges[rank][1])]
         self.role = "input" if rank == 0 else ("output" if rank == world_size - 1 else "middle")
-        self.items = 0
-        self._posted_first = False
+        self.items = 0            # chunks processed (stage 0: sent)
+        self.received = 0         # stage 0: packets taken from the closing edge
+        self._returned = deque()  # stage 0: packets taken in by quiesce(), not yet adopted
 
     @property
     def owned_blocks(self) -> range:
@@ -39,21 +41,28 @@ class PipelineStageRunner:
 
     # ------------------------------------------------------------------ one chunk on this rank
     def step(self, chunk_idx: int = 0, noise: Optional[torch.Tensor] = None, current_start: Optional[int] = None,
-             current_end: Optional[int] = None, current_step: Optional[int] = None) -> Optional[torch.Tensor]:
+             current_end: Optional[int] = None, current_step: Optional[int] = None,
+             last: bool = False) -> Optional[torch.Tensor]:
         """Process one chunk on this rank.  Stage 0 needs `noise`, `current_start`, `current_end`
         (and optionally the adaptive `current_step`); the other stages take everything from the
-        packet they receive.  The last stage returns the denoised stage batch, the others None."""
+        packet they receive.  The last stage returns the denoised stage batch, the others None.
+        `last=True` marks the final chunk before `quiesce()`: no receive is posted ahead."""
         pipe, link = self.pipe, self.link
         if self.role == "input":
             if self.items >= self.world:
-                back = link.recv()                      # what the last stage made of chunk items-world
-                link.post_recv()
+                if self._returned:
+                    back = self._returned.popleft()     # taken in early by quiesce()
+                else:
+                    back = link.recv()                  # what the last stage made of chunk items-world
+                    self.received += 1
+                    if not last:
+                        link.post_recv()
                 pipe.hidden_states.copy_(back.latents)
                 pipe.kv_cache_starts.copy_(torch.tensor(back.starts, dtype=torch.long), non_blocking=True)
                 pipe.kv_cache_ends.copy_(torch.tensor(back.ends, dtype=torch.long), non_blocking=True)
                 pipe._starts_host = list(back.starts)
                 pipe._ends_host = list(back.ends)
-            elif self.items == self.world - 1:
+            elif self.items == self.world - 1 and not last:
                 link.post_recv()
             act, _ = pipe.inference(noise=noise, current_start=current_start, current_end=current_end,
                                     current_step=current_step, block_mode="input", block_num=self.block_range)
@@ -63,7 +72,8 @@ class PipelineStageRunner:
             return None
 
         pkt: StagePacket = link.recv()
-        link.post_recv()
+        if not last:
+            link.post_recv()
         step = None if pkt.current_step < 0 else pkt.current_step
         out, pshape = pipe.inference(noise=pkt.latents, current_start=pkt.starts, current_end=pkt.ends,
                                      current_step=step, block_mode=self.role, block_num=self.block_range,
@@ -77,10 +87,19 @@ class PipelineStageRunner:
         self.items += 1
         return out
 
-    def finish(self) -> None:
-        """Stage 0 takes in the packets still travelling back to it; everyone waits for its sends."""
+    def quiesce(self) -> None:
+        """Empty the ring: stage 0 takes in every packet still travelling back to it (they are kept
+        and adopted in order by the following steps), every stage waits for its sends.  Afterwards
+        no transfer is posted or in flight, so a device-wide synchronise or a barrier cannot wait
+        on a peer.  The step before it must have been run with `last=True` on every rank."""
         if self.role == "input":
-            # the last stage returns one packet per chunk; items - world of them were taken in
-            for _ in range(self.items - max(self.items - self.world, 0)):
-                self.link.recv()
+            while self.received < self.items:          # one packet comes back per chunk sent
+                pkt = self.link.recv()
+                self.received += 1
+                self._returned.append(StagePacket(pkt.chunk_idx, pkt.current_step, pkt.patched_x_shape, pkt.starts,
+                                                  pkt.ends, None, pkt.latents.clone()))
         self.link.drain()
+
+    def finish(self) -> None:
+        """End of stream: same as quiesce()."""
+        self.quiesce()

@@ -107,6 +107,27 @@ class StageLink:
                           self.device)
         self._up_has_act, self._down_has_act = not closing_up, not closing_down
         self._side = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+        self._warm_edges(dtype)
+
+    def _warm_edges(self, dtype) -> None:
+        """Create every edge's communicator now, one edge at a time, with nothing else in flight.
+        A communicator that is created lazily by its first transfer blocks the host (and may
+        synchronise the device) while another edge's receive is already waiting on the GPU for a
+        send this host has not issued yet; two stages doing that to each other never finish."""
+        for i in range(self.world):
+            src, dst = i, (i + 1) % self.world
+            if self.rank in (src, dst):
+                t = torch.zeros(8, dtype=dtype, device=self.device)
+                m = torch.zeros(2, dtype=torch.int64)
+                if self.rank == src:
+                    dist.send(m, dst=dst, group=self._meta_groups[i])
+                    dist.send(t, dst=dst, group=self._edge_groups[i])
+                else:
+                    dist.recv(m, src=src, group=self._meta_groups[i])
+                    dist.recv(t, src=src, group=self._edge_groups[i])
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            dist.barrier()
 
     # ------------------------------------------------------------------ receive side
     def post_recv(self) -> None:
@@ -173,9 +194,13 @@ class StageLink:
 
     def drain(self) -> None:
         """Wait for every outstanding send (call before tearing the process group down)."""
-        for e in (self.down,):
-            for w in list(e.works) + list(e.meta_works):
-                if w is not None:
-                    w.wait()
+        e = self.down
+        for i in range(len(e.bufs)):           # a finished work must not be waited on twice
+            if e.works[i] is not None:
+                e.works[i].wait()
+                e.works[i] = None
+            if e.meta_works[i] is not None:
+                e.meta_works[i].wait()
+                e.meta_works[i] = None
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)

@@ -41,7 +41,7 @@ class _Patch:
         setattr(obj, name, value)
 
 
-def _worker_pipeline(rank, world, port, ranges, q):
+def _worker_pipeline(rank, world, port, ranges, quiesce_every, q):
     try:
         _init(rank, world, port)
         import fake_ops
@@ -64,9 +64,12 @@ def _worker_pipeline(rank, world, port, ranges, q):
             runner = PipelineStageRunner(pipe, link, rank, world, ranges)
             outs, states = [], []
             for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
-                o = runner.step(i, noise, cs, ce, None)
+                last = quiesce_every > 0 and i % quiesce_every == quiesce_every - 1
+                o = runner.step(i, noise, cs, ce, None, last=last)
                 if o is not None:
                     outs.append(o.clone().numpy())
+                if last:
+                    runner.quiesce()       # ring emptied mid-stream; results must not change
                 states.append(snapshot(pipe, runner.block_range[0] if rank == 0 else runner.block_range[1] - 1))
             runner.finish()
         q.put((rank, "ok", outs, states))
@@ -97,11 +100,12 @@ def _run(target, world, *args, timeout=240):
     return results
 
 
-def test_two_rank_pipeline_matches_reference_fixture():
+@pytest.mark.parametrize("quiesce_every", [0, 3])
+def test_two_rank_pipeline_matches_reference_fixture(quiesce_every):
     case = cases.MODEL_CASES["m_stages"]
     meta, z = cases.load_fixture("m_stages")
     nblk, split = cases.MODEL_KW["num_layers"], case["split"]
-    res = _run(_worker_pipeline, 2, [[0, split], [split, nblk]])
+    res = _run(_worker_pipeline, 2, [[0, split], [split, nblk]], quiesce_every)
     for r, v in res.items():
         assert v[0] == "ok", v[1]
     outs = res[1][1]
@@ -117,7 +121,7 @@ def test_two_rank_pipeline_matches_reference_fixture():
 def test_three_rank_pipeline_runs_with_a_middle_stage():
     """input -> middle -> output over three ranks; index state must stay consistent on every stage
     (all stages see the same row starts) and the stream must complete."""
-    res = _run(_worker_pipeline, 3, [[0, 1], [1, 2], [2, 3]])
+    res = _run(_worker_pipeline, 3, [[0, 1], [1, 2], [2, 3]], 4)
     for r, v in res.items():
         assert v[0] == "ok", v[1]
     n = cases.MODEL_CASES["m_stages"]["chunks"]
