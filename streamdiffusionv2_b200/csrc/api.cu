@@ -84,7 +84,7 @@ int make_square_map(CUtensorMap* tm, const void* ptr) {
   return SDV2_OK;
 }
 
-constexpr size_t kStatusBytes = 256;
+constexpr size_t kStatusBytes = sdv2::kAttnStatusBytes;
 
 int attn_common(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, const sdv2_view* out, int rows,
                 int q_tokens, int heads, int head_dim, int64_t kv_extent, const int32_t* seq_lens,
@@ -119,6 +119,11 @@ int attn_common(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, cons
   p.kv_row_broadcast = (k->stride_row == 0) ? 1 : 0;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = static_cast<int*>(workspace);
+  // scratch for split tail tiles, when the caller's workspace has room for it
+  if (workspace_bytes >= kStatusBytes + sdv2::kAttnMaxPartialSlots * sdv2::kAttnPartialBytesPerSlot) {
+    p.part_ml = reinterpret_cast<float*>(static_cast<char*>(workspace) + kStatusBytes);
+    p.part_o = p.part_ml + static_cast<size_t>(sdv2::kAttnMaxPartialSlots) * 2 * 2 * 128;
+  }
 
   CUtensorMap tm_q, tm_k, tm_v;
   if ((rc = make_tile_map(&tm_q, q, rows, q_tokens, heads)) != SDV2_OK) return rc;
@@ -208,7 +213,8 @@ int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view*
 
 size_t sdv2_attn_workspace_bytes(int rows, int q_tokens, int heads, int head_dim) {
   (void)rows; (void)q_tokens; (void)heads; (void)head_dim;
-  return kStatusBytes;
+  // status block + scratch for the partial results of split tail tiles (at most one per SM)
+  return kStatusBytes + sdv2::kAttnMaxPartialSlots * sdv2::kAttnPartialBytesPerSlot;
 }
 
 int sdv2_attn_kvcache(const sdv2_view* q, const sdv2_view* k_cache, const sdv2_view* v_cache,

@@ -55,6 +55,7 @@ constexpr uint32_t kIdescQK = umma_idesc_bf16(kBM, kBN, false, false);
 constexpr uint32_t kIdescPV = umma_idesc_bf16(kBM, kHD, false, true);
 
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr int kMinKvTilesForSplit = 16;
 
 // S[stage] = Q[stage] (128 x 128, K-major) * K_tile^T (128 x 128, K-major); 8 steps of K = 16.
 __device__ __forceinline__ void issue_qk(uint32_t tmem_s, uint32_t sq, uint32_t sk) {
@@ -89,12 +90,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
   const int lane = threadIdx.x & 31;
 
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
-  const int q0 = blockIdx.x * (2 * kBM);
+  // work item: a whole (query tile pair, head, row) tile, or one key range of a tail tile
+  int tile = blockIdx.x, part = -1;
+  if (tile >= p.n_full) {
+    const int r = tile - p.n_full;
+    tile = p.n_full + r / p.split;
+    part = r - (r / p.split) * p.split;
+  }
+  const int pt = tile % p.pair_tiles;
+  const int hb = tile / p.pair_tiles;
+  const int h = hb % p.heads;
+  const int b = hb / p.heads;
+  const int q0 = pt * (2 * kBM);
   const bool two_tiles = q0 + kBM < p.q_tokens;
   const int seq_len = p.seq_lens[b];
-  const int n_kv = (seq_len + kBN - 1) / kBN;
+  const int n_kv_all = (seq_len + kBN - 1) / kBN;
+  const int j0 = part < 0 ? 0 : static_cast<int>(static_cast<int64_t>(part) * n_kv_all / p.split);
+  const int j1 = part < 0 ? n_kv_all : static_cast<int>(static_cast<int64_t>(part + 1) * n_kv_all / p.split);
+  const int n_kv = j1 - j0;  // key tiles of this item (the host keeps split <= n_kv_all, so >= 1)
   const int bk = p.kv_row_broadcast ? 0 : b;
 
   if (threadIdx.x == 0) {
@@ -143,8 +156,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
         const uint32_t dst = base + kSmemKV + slot * kTileBytes;
         mbar_expect_tx(bar(kBarKvFull + slot), kTileBytes);
-        tma_load_4d(dst, tm, bar(kBarKvFull + slot), 0, h, (it >> 1) * kBN, bk);
-        tma_load_4d(dst + kHalfTile, tm, bar(kBarKvFull + slot), 64, h, (it >> 1) * kBN, bk);
+        tma_load_4d(dst, tm, bar(kBarKvFull + slot), 0, h, (j0 + (it >> 1)) * kBN, bk);
+        tma_load_4d(dst + kHalfTile, tm, bar(kBarKvFull + slot), 64, h, (j0 + (it >> 1)) * kBN, bk);
         issued = it + 1;
       }
       if (!ok) {
@@ -222,7 +235,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, s[c]);
         tmem_wait_ld();
-        const int valid = seq_len - j * kBN;
+        const int valid = seq_len - (j0 + j) * kBN;
         if (valid < kBN) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -285,7 +298,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = mbar_wait(bar(kBarOFull + stage), 0, abort_flag, p.status, WAIT_O_FULL);
         ok = __all_sync(0xffffffffu, ok);
       }
-      if (ok) {
+      if (ok && part < 0) {
         tc_fence_after();
         const float inv = 1.f / l;
         const int q_row = q0 + stage * kBM + row;
@@ -308,6 +321,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               *reinterpret_cast<uint4*>(op + c * 32 + i * 8) = v;
             }
           }
+        }
+      } else if (ok) {
+        // partial result of one key range: unnormalised accumulator, running max and sum
+        tc_fence_after();
+        const int slot = (tile - p.n_full) * p.split + part;
+        float* po = p.part_o + (static_cast<size_t>(slot) * 2 + stage) * (kBM * kHD) + row * kHD;
+        float* pml = p.part_ml + (static_cast<size_t>(slot) * 2 + stage) * (2 * kBM);
+        pml[row] = m_used;
+        pml[kBM + row] = l;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<uint4*>(po + c * 32 + i * 4) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
         }
       }
     }
@@ -421,14 +451,87 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 
 }  // namespace attn
 
+// Merge the partial results of the split tail tiles: one block per (tail tile, query tile), one
+// thread per query row.  out = sum_k 2^(m_k - m) O_k / sum_k 2^(m_k - m) l_k.
+__global__ void __launch_bounds__(attn::kBM) attn_combine_kernel(const __grid_constant__ AttnParams p) {
+  using namespace attn;
+  const int tail = blockIdx.x, stage = blockIdx.y, row = threadIdx.x;
+  const int tile = p.n_full + tail;
+  const int pt = tile % p.pair_tiles;
+  const int hb = tile / p.pair_tiles;
+  const int h = hb % p.heads;
+  const int b = hb / p.heads;
+  const int q_row = pt * (2 * kBM) + stage * kBM + row;
+  if (q_row >= p.q_tokens) return;
+  const float* ml = p.part_ml + (static_cast<size_t>(tail) * p.split * 2 + stage) * (2 * kBM);
+  const float* po = p.part_o + (static_cast<size_t>(tail) * p.split * 2 + stage) * (kBM * kHD) + row * kHD;
+  const size_t ml_step = 2 * 2 * kBM, po_step = static_cast<size_t>(2) * kBM * kHD;
+  float m = -INFINITY;
+  for (int k = 0; k < p.split; ++k) m = fmaxf(m, ml[k * ml_step + row]);
+  float l = 0.f;
+  for (int k = 0; k < p.split; ++k) l += exp2f(ml[k * ml_step + row] - m) * ml[k * ml_step + kBM + row];
+  const float inv = 1.f / l;
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(b) * p.out_stride_row +
+                      static_cast<int64_t>(q_row) * p.out_stride_tok + static_cast<int64_t>(h) * p.out_stride_head;
+#pragma unroll 1
+  for (int c = 0; c < kHD; c += 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < p.split; ++k) {
+      const float w = exp2f(ml[k * ml_step + row] - m);
+      const float4 a = *reinterpret_cast<const float4*>(po + k * po_step + c);
+      const float4 d = *reinterpret_cast<const float4*>(po + k * po_step + c + 4);
+      acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
+      acc[4] += w * d.x; acc[5] += w * d.y; acc[6] += w * d.z; acc[7] += w * d.w;
+    }
+    uint4 v;
+    v.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+    v.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+    v.z = pack_bf16x2(acc[4] * inv, acc[5] * inv);
+    v.w = pack_bf16x2(acc[6] * inv, acc[7] * inv);
+    *reinterpret_cast<uint4*>(op + c) = v;
+  }
+}
+
 cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
-                                const AttnParams& p, cudaStream_t stream) {
+                                const AttnParams& p_in, cudaStream_t stream) {
+  AttnParams p = p_in;
   // per device and cheap, so set on every launch rather than cached per process
-  cudaError_t attr = cudaFuncSetAttribute(attn::attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(attn::kSmemBytes));
-  if (attr != cudaSuccess) return attr;
-  dim3 grid((p.q_tokens + 2 * attn::kBM - 1) / (2 * attn::kBM), p.heads, p.rows);
+  cudaError_t e = cudaFuncSetAttribute(attn::attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(attn::kSmemBytes));
+  if (e != cudaSuccess) return e;
+  int dev = 0, sms = 0;
+  e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return e;
+  p.pair_tiles = (p.q_tokens + 2 * attn::kBM - 1) / (2 * attn::kBM);
+  const int64_t n_tiles = static_cast<int64_t>(p.pair_tiles) * p.heads * p.rows;
+  if (n_tiles > 0x7FFFFFFFLL) return cudaErrorInvalidValue;
+  // One CTA per SM: with n_tiles = w * sms + tail the last wave keeps only `tail` SMs busy.  Cut each of
+  // its tiles into `split` key ranges so that the last wave takes 1/split of a tile time.
+  int min_kv = 0x7FFFFFFF;
+  for (int b = 0; b < p.rows; ++b) min_kv = min(min_kv, (p.seq_lens[b] + attn::kBN - 1) / attn::kBN);
+  p.n_full = static_cast<int>(n_tiles);
+  p.n_tail = 0;
+  p.split = 1;
+  const int tail = static_cast<int>(n_tiles % sms);
+  // (worth a second launch only when a tile is long: short key ranges, e.g. the 4 tiles of the text
+  // context, are dominated by per-CTA set-up)
+  if (p.part_o != nullptr && tail > 0 && min_kv >= attn::kMinKvTilesForSplit) {
+    int split = sms / tail;
+    if (split > min_kv) split = min_kv;
+    if (split > 32) split = 32;
+    while (split >= 2 && tail * split > kAttnMaxPartialSlots) --split;
+    if (split >= 2) {
+      p.n_tail = tail;
+      p.n_full = static_cast<int>(n_tiles) - tail;
+      p.split = split;
+    }
+  }
+  const unsigned grid = static_cast<unsigned>(p.n_full + p.n_tail * p.split);
   attn::attn_fwd_kernel<<<grid, attn::kThreads, attn::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess || p.n_tail == 0) return e;
+  attn_combine_kernel<<<dim3(p.n_tail, 2), attn::kBM, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

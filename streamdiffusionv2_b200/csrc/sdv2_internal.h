@@ -38,8 +38,18 @@ struct AttnParams {
   int kv_row_broadcast;  // 1: every row reads K/V row 0 (stride-0 expand)
   float scale_log2;      // softmax_scale * log2(e)
   int* status;           // first word of the workspace
+  // tail split: tiles [0, n_full) run whole; each of the n_tail tiles after them is cut into `split`
+  // key ranges whose partial results (unnormalised O, running max, running sum) go to scratch
+  int pair_tiles;        // query tile pairs per (head, row)
+  int n_full, n_tail, split;
+  float* part_o;         // [n_tail * split][2][128][128] fp32
+  float* part_ml;        // [n_tail * split][2][2][128] fp32: max (log2 units), sum
   int seq_lens[SDV2_MAX_ROWS];
 };
+
+constexpr int kAttnMaxPartialSlots = 192;
+constexpr size_t kAttnStatusBytes = 256;
+constexpr size_t kAttnPartialBytesPerSlot = 2 * 128 * 128 * 4 + 2 * 2 * 128 * 4;
 
 cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                                 const AttnParams& p, cudaStream_t stream);
