@@ -135,6 +135,31 @@ int sdv2_attn_kvcache_simt(const sdv2_view* q, const sdv2_view* k_cache, const s
                            int64_t cache_tokens, const int32_t* seq_lens, float softmax_scale,
                            int dtype, void* stream);
 
+/*
+ * sdv2_attn_kvcache without a caller-provided workspace.  No counterpart in the reference (which
+ * lets PyTorch allocate whatever its kernels need): this entry point exists for hosts that cannot
+ * give the library scratch memory - embedders that only hold borrowed tensor pointers, workers
+ * whose device memory was fully partitioned at start-up, loops where a cudaMalloc in the per-chunk
+ * path would serialise the GPU.  The status block and the partial results of the split tail tiles
+ * live in a device array built into the library (24.4 MiB per GPU, 192 partial slots).
+ *
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *  - The first call on each device resolves the array's address and zeroes its status block; that
+ *    call synchronises, so make it before any stream capture starts.
+ *  - A problem whose tail split needs more than 192 partial slots is refused with
+ *    SDV2_ERR_WORKSPACE before anything is launched; rows > SDV2_MAX_ROWS with
+ *    SDV2_ERR_UNSUPPORTED_SHAPE.
+ *  - All calls on a device share the array and it keeps the previous call's contents (every slot is
+ *    rewritten before it is read).  Calls that overlap on the GPU race on it: order them.
+ *  - status_dev_out (optional) receives the device address of the status block, valid for
+ *    sdv2_read_status.
+ * Results are identical to sdv2_attn_kvcache on the same inputs.
+ */
+int sdv2_attn_kvcache_static(const sdv2_view* q, const sdv2_view* k_cache, const sdv2_view* v_cache,
+                             const sdv2_view* out, int rows, int q_tokens, int heads, int head_dim,
+                             int64_t cache_tokens, const int32_t* seq_lens, float softmax_scale,
+                             void** status_dev_out, void* stream);
+
 /* Synchronises `stream`, reads the status word at the start of a workspace and clears it.
  * Returns SDV2_OK, SDV2_ERR_TIMEOUT (a device-side wait ran out; *detail = where) or
  * SDV2_ERR_CUDA. */

@@ -48,6 +48,9 @@ _SIGNATURES = {
     "sdv2_attn_kvcache_simt": (C.c_int, [C.POINTER(View)] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64,
                                                                   C.POINTER(C.c_int32), C.c_float, C.c_int,
                                                                   C.c_void_p]),
+    "sdv2_attn_kvcache_static": (C.c_int, [C.POINTER(View)] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64,
+                                                                    C.POINTER(C.c_int32), C.c_float,
+                                                                    C.POINTER(C.c_void_p), C.c_void_p]),
     "sdv2_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.c_void_p]),
     "sdv2_selftest_umma": (C.c_int, [C.c_void_p] * 4 + [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
