@@ -451,11 +451,14 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 
 }  // namespace attn
 
-// Merge the partial results of the split tail tiles: one block per (tail tile, query tile), one
-// thread per query row.  out = sum_k 2^(m_k - m) O_k / sum_k 2^(m_k - m) l_k.
-__global__ void __launch_bounds__(attn::kBM) attn_combine_kernel(const __grid_constant__ AttnParams p) {
+// Merge the partial results of the split tail tiles.  Block = (tail tile, query tile, group of 32
+// rows); 256 threads = 32 rows x 8 column groups of 16, so the 8 threads of a row read its 512
+// bytes of each partial accumulator contiguously.  out = sum_k 2^(m_k - m) O_k / sum_k 2^(m_k - m) l_k.
+__global__ void __launch_bounds__(256) attn_combine_kernel(const __grid_constant__ AttnParams p) {
   using namespace attn;
-  const int tail = blockIdx.x, stage = blockIdx.y, row = threadIdx.x;
+  const int tail = blockIdx.x, stage = blockIdx.y;
+  const int row = blockIdx.z * 32 + (threadIdx.x >> 3);
+  const int c0 = (threadIdx.x & 7) * 16;
   const int tile = p.n_full + tail;
   const int pt = tile % p.pair_tiles;
   const int hb = tile / p.pair_tiles;
@@ -464,31 +467,34 @@ __global__ void __launch_bounds__(attn::kBM) attn_combine_kernel(const __grid_co
   const int q_row = pt * (2 * kBM) + stage * kBM + row;
   if (q_row >= p.q_tokens) return;
   const float* ml = p.part_ml + (static_cast<size_t>(tail) * p.split * 2 + stage) * (2 * kBM);
-  const float* po = p.part_o + (static_cast<size_t>(tail) * p.split * 2 + stage) * (kBM * kHD) + row * kHD;
+  const float* po = p.part_o + (static_cast<size_t>(tail) * p.split * 2 + stage) * (kBM * kHD) + row * kHD + c0;
   const size_t ml_step = 2 * 2 * kBM, po_step = static_cast<size_t>(2) * kBM * kHD;
   float m = -INFINITY;
   for (int k = 0; k < p.split; ++k) m = fmaxf(m, ml[k * ml_step + row]);
   float l = 0.f;
-  for (int k = 0; k < p.split; ++k) l += exp2f(ml[k * ml_step + row] - m) * ml[k * ml_step + kBM + row];
+  float acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+  for (int k = 0; k < p.split; ++k) {
+    const float w = exp2f(ml[k * ml_step + row] - m);
+    l += w * ml[k * ml_step + kBM + row];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 a = *reinterpret_cast<const float4*>(po + k * po_step + 4 * i);
+      acc[4 * i + 0] += w * a.x; acc[4 * i + 1] += w * a.y; acc[4 * i + 2] += w * a.z; acc[4 * i + 3] += w * a.w;
+    }
+  }
   const float inv = 1.f / l;
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(b) * p.out_stride_row +
-                      static_cast<int64_t>(q_row) * p.out_stride_tok + static_cast<int64_t>(h) * p.out_stride_head;
-#pragma unroll 1
-  for (int c = 0; c < kHD; c += 8) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < p.split; ++k) {
-      const float w = exp2f(ml[k * ml_step + row] - m);
-      const float4 a = *reinterpret_cast<const float4*>(po + k * po_step + c);
-      const float4 d = *reinterpret_cast<const float4*>(po + k * po_step + c + 4);
-      acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
-      acc[4] += w * d.x; acc[5] += w * d.y; acc[6] += w * d.z; acc[7] += w * d.w;
-    }
+                      static_cast<int64_t>(q_row) * p.out_stride_tok + static_cast<int64_t>(h) * p.out_stride_head + c0;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
     uint4 v;
-    v.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
-    v.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
-    v.z = pack_bf16x2(acc[4] * inv, acc[5] * inv);
-    v.w = pack_bf16x2(acc[6] * inv, acc[7] * inv);
-    *reinterpret_cast<uint4*>(op + c) = v;
+    v.x = pack_bf16x2(acc[8 * i + 0] * inv, acc[8 * i + 1] * inv);
+    v.y = pack_bf16x2(acc[8 * i + 2] * inv, acc[8 * i + 3] * inv);
+    v.z = pack_bf16x2(acc[8 * i + 4] * inv, acc[8 * i + 5] * inv);
+    v.w = pack_bf16x2(acc[8 * i + 6] * inv, acc[8 * i + 7] * inv);
+    *reinterpret_cast<uint4*>(op + 8 * i) = v;
   }
 }
 
@@ -531,7 +537,7 @@ cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k
   attn::attn_fwd_kernel<<<grid, attn::kThreads, attn::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
   e = cudaGetLastError();
   if (e != cudaSuccess || p.n_tail == 0) return e;
-  attn_combine_kernel<<<dim3(p.n_tail, 2), attn::kBM, 0, stream>>>(p);
+  attn_combine_kernel<<<dim3(p.n_tail, 2, attn::kBM / 32), 256, 0, stream>>>(p);
   return cudaGetLastError();
 }
 
