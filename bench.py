@@ -145,7 +145,7 @@ def run_reference_arm(args):
     sample = (f"attention path only (rope + slot write + attention over the full 32760-token cache), 1 of 30 "
               f"layers, 2 cache rows, {q_tokens} of 3120 query tokens per row timed and scaled; chunk time = 30 x "
               f"layer time; linear layers, norms and FFN not included")
-    line = {"impl": "reference", "metric": "streaming_fps_480x832_wan1.3b", "value": fps, "unit": "video frames/s",
+    line = {"impl": "reference", "metric": metric_name(), "value": fps, "unit": "video frames/s",
             "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": chunk_s * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 storage, fp32 math",
             "data": "synthetic", "config": workload_config(args.gpus),
@@ -155,9 +155,14 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
+def metric_name():
+    return "streaming_fps_480x832_wan1.3b" if MODEL_1P3B["dim"] == 1536 else "streaming_fps_480x832_wan14b"
+
+
 def workload_config(n_gpus: int):
-    return {"workload": "config 2: random-init causal Wan-1.3B DiT, 480x832, 2 denoise levels (2 cache rows), "
-                        "2 latent frames per chunk, 1 sink + 20 ring frame cache, full and wrapping",
+    name = "Wan-1.3B" if MODEL_1P3B["dim"] == 1536 else "Wan-14B"
+    return {"workload": f"random-init causal {name} DiT, 480x832, {len(LEVELS)} denoise levels ({len(LEVELS)} cache "
+                        "rows), 2 latent frames per chunk, 1 sink + 20 ring frame cache, full and wrapping",
             "tokens_per_chunk_row": FRAMES_PER_CHUNK * FRAME_TOKENS, "cache_tokens": CACHE_FRAMES * FRAME_TOKENS,
             "cache_rows": len(LEVELS), "blocks": MODEL_1P3B["num_layers"],
             "parallelism": "single GPU" if n_gpus == 1 else f"pipeline of {n_gpus} contiguous block ranges",
@@ -287,7 +292,7 @@ def run_single_gpu(args):
                "sample": f"attention path only, 1 of 30 layers, 2 cache rows, 780 of 3120 query tokens per row timed "
                          f"and scaled, {len(times)} samples; chunk time = 30 x layer time; linear layers not included"}
     line = {
-        "metric": "streaming_fps_480x832_wan1.3b", "value": fps, "unit": "video frames/s", "n_gpus": 1,
+        "metric": metric_name(), "value": fps, "unit": "video frames/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(1),
@@ -410,7 +415,7 @@ def run_pipeline(args):
         achieved = att_flops / (att_ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
         line = {
-            "metric": "streaming_fps_480x832_wan1.3b", "value": VIDEO_FRAMES_PER_CHUNK * args.steps / (ms_max / 1e3),
+            "metric": metric_name(), "value": VIDEO_FRAMES_PER_CHUNK * args.steps / (ms_max / 1e3),
             "unit": "video frames/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
@@ -435,7 +440,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model", default="1.3b", choices=["1.3b", "14b"],
+                    help="1.3b is the headline workload; 14b = 40 blocks, dim 5120, 40 heads, 4 denoise levels")
     args = ap.parse_args()
+    if args.model == "14b":
+        MODEL_1P3B.update(dim=5120, ffn_dim=13824, num_heads=40, num_layers=40)
+        LEVELS[:] = [1000, 750, 500, 250]
     args.warmup = max(args.warmup, 0)
     if args.impl == "reference":
         return run_reference_arm(args)
