@@ -324,7 +324,7 @@ def run_pipeline(args):
     local = int(os.environ.get("LOCAL_RANK", rank))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    dist.init_process_group("nccl", device_id=device)
+    dist.init_process_group("nccl")   # lazy communicators: the stage links create theirs one edge at a time
     peaks = measured_peaks()
     pipe = build_pipeline(device)
     ranges = contiguous_block_ranges(MODEL_1P3B["num_layers"], world)
@@ -342,7 +342,7 @@ def run_pipeline(args):
     n_tok = FRAMES_PER_CHUNK * FRAME_TOKENS
 
     def barrier():
-        dist.barrier()
+        dist.barrier(device_ids=[local])
         torch.cuda.synchronize()
 
     with torch.no_grad():

@@ -127,7 +127,9 @@ class StageLink:
                     dist.recv(t, src=src, group=self._edge_groups[i])
             if self.device.type == "cuda":
                 torch.cuda.synchronize(self.device)
-            dist.barrier()
+                dist.barrier(device_ids=[self.device.index])
+            else:
+                dist.barrier()
 
     # ------------------------------------------------------------------ receive side
     def post_recv(self) -> None:
