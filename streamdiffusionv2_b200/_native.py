@@ -51,6 +51,10 @@ _SIGNATURES = {
     "sdv2_attn_kvcache_static": (C.c_int, [C.POINTER(View)] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64,
                                                                     C.POINTER(C.c_int32), C.c_float,
                                                                     C.POINTER(C.c_void_p), C.c_void_p]),
+    "sdv2_rmsnorm": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int,
+                               C.c_float, C.c_void_p]),
+    "sdv2_ln_modulate": (C.c_int, [C.c_void_p] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p]),
+    "sdv2_gate_residual": (C.c_int, [C.c_void_p] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "sdv2_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.c_void_p]),
     "sdv2_selftest_umma": (C.c_int, [C.c_void_p] * 4 + [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }

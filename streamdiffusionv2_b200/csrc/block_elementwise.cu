@@ -1,0 +1,246 @@
+// Fused element-wise kernels for the operations directly around the attention path of a DiT block
+// (bf16 tensors, fp32 statistics).  Each replaces a chain of PyTorch element-wise launches and
+// reproduces that chain's intermediate bf16 roundings, so the values handed to the projections and
+// to the cache kernels are the ones the unfused chain would produce.
+//
+//   rmsnorm        : bf16( bf16(x * rsqrt(mean(x^2) + eps)) * w )                     per token row
+//   ln_modulate    : bf16( bf16( bf16(LN(x)) * scale1p[b, frame] ) + shift[b, frame] )  per token row
+//   gate_residual  : bf16( x + bf16(y * gate[b, frame]) )                              per element
+//
+// All three are pure streaming kernels (one read and one write of [tokens, dim], plus y for the
+// last), bound by HBM bandwidth; 16-byte vector accesses, one token row per block for the two
+// normalisations.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+#include "sdv2_internal.h"
+
+namespace sdv2 {
+
+constexpr int kRowThreads = 256;
+constexpr int kMaxVecPerThread = 4;  // dim <= 256 * 4 * 8 = 8192
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float lo_f(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_f(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // red may still be read from a previous call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < (kRowThreads / 32) ? red[lane] : 0.f;
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+
+struct RowParams {
+  const __nv_bfloat16* x;
+  __nv_bfloat16* out;
+  int64_t x_stride, out_stride;  // elements between token rows
+  int64_t n_rows;
+  int dim;
+  float eps;
+  const __nv_bfloat16* w;        // rmsnorm weight [dim]
+  const __nv_bfloat16* scale1p;  // ln_modulate: (1 + scale) [batch, frames, dim]
+  const __nv_bfloat16* shift;    // ln_modulate: shift [batch, frames, dim]
+  int tokens_per_batch, tokens_per_frame, frames;
+};
+
+template <bool kLayerNorm>
+__global__ void __launch_bounds__(kRowThreads) row_norm_kernel(const __grid_constant__ RowParams p) {
+  __shared__ float red[kRowThreads / 32];
+  const int64_t row = blockIdx.x;
+  const int n_vec = p.dim >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(p.x + row * p.x_stride);
+  uint4 v[kMaxVecPerThread];
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxVecPerThread; ++i) {
+    const int c = threadIdx.x + i * kRowThreads;
+    if (c < n_vec) {
+      v[i] = xr[c];
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = lo_f(w[j]), b = hi_f(w[j]);
+        s += a + b;
+        ss += a * a + b * b;
+      }
+    }
+  }
+  float mean = 0.f, rstd;
+  if (kLayerNorm) {
+    mean = block_sum(s, red) / p.dim;
+    // second pass over the registers for the variance: sum (x - mean)^2
+    float d2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerThread; ++i) {
+      const int c = threadIdx.x + i * kRowThreads;
+      if (c < n_vec) {
+        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = lo_f(w[j]) - mean, b = hi_f(w[j]) - mean;
+          d2 += a * a + b * b;
+        }
+      }
+    }
+    rstd = rsqrtf(block_sum(d2, red) / p.dim + p.eps);
+  } else {
+    rstd = rsqrtf(block_sum(ss, red) / p.dim + p.eps);
+  }
+  const uint4* mul = nullptr;
+  const uint4* add = nullptr;
+  if (kLayerNorm) {
+    const int64_t b = row / p.tokens_per_batch;
+    const int f = static_cast<int>((row - b * p.tokens_per_batch) / p.tokens_per_frame);
+    const int64_t off = (b * p.frames + f) * p.dim;
+    mul = reinterpret_cast<const uint4*>(p.scale1p + off);
+    add = reinterpret_cast<const uint4*>(p.shift + off);
+  } else {
+    mul = reinterpret_cast<const uint4*>(p.w);
+  }
+  uint4* orow = reinterpret_cast<uint4*>(p.out + row * p.out_stride);
+#pragma unroll
+  for (int i = 0; i < kMaxVecPerThread; ++i) {
+    const int c = threadIdx.x + i * kRowThreads;
+    if (c < n_vec) {
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+      const uint4 m4 = __ldg(mul + c);
+      const uint32_t m[4] = {m4.x, m4.y, m4.z, m4.w};
+      uint32_t a4[4] = {0, 0, 0, 0};
+      if (kLayerNorm) {
+        const uint4 t = __ldg(add + c);
+        a4[0] = t.x; a4[1] = t.y; a4[2] = t.z; a4[3] = t.w;
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float lo = bf16_round((lo_f(w[j]) - mean) * rstd);
+        float hi = bf16_round((hi_f(w[j]) - mean) * rstd);
+        lo = lo * lo_f(m[j]);
+        hi = hi * hi_f(m[j]);
+        if (kLayerNorm) {
+          lo = bf16_round(lo) + lo_f(a4[j]);
+          hi = bf16_round(hi) + hi_f(a4[j]);
+        }
+        o[j] = pack_bf16x2(lo, hi);
+      }
+      orow[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+struct GateParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* y;
+  const __nv_bfloat16* gate;  // [batch, frames, dim]
+  __nv_bfloat16* out;
+  int64_t n_rows;
+  int dim, tokens_per_batch, tokens_per_frame, frames;
+};
+
+__global__ void __launch_bounds__(256) gate_residual_kernel(const __grid_constant__ GateParams p) {
+  const int n_vec = p.dim >> 3;
+  const int64_t total = p.n_rows * n_vec;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / n_vec;
+    const int c = static_cast<int>(i - row * n_vec);
+    const int64_t b = row / p.tokens_per_batch;
+    const int f = static_cast<int>((row - b * p.tokens_per_batch) / p.tokens_per_frame);
+    const uint4 xv = reinterpret_cast<const uint4*>(p.x)[i];
+    const uint4 yv = reinterpret_cast<const uint4*>(p.y)[i];
+    const uint4 gv = __ldg(reinterpret_cast<const uint4*>(p.gate + (b * p.frames + f) * p.dim) + c);
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, yw[4] = {yv.x, yv.y, yv.z, yv.w},
+                   gw[4] = {gv.x, gv.y, gv.z, gv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = lo_f(xw[j]) + bf16_round(lo_f(yw[j]) * lo_f(gw[j]));
+      const float hi = hi_f(xw[j]) + bf16_round(hi_f(yw[j]) * hi_f(gw[j]));
+      o[j] = pack_bf16x2(lo, hi);
+    }
+    reinterpret_cast<uint4*>(p.out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+}  // namespace sdv2
+
+namespace {
+bool a16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+}
+
+extern "C" int sdv2_rmsnorm(const void* x, int64_t x_row_stride, const void* weight, void* out,
+                            int64_t out_row_stride, int64_t n_rows, int dim, float eps, void* stream) {
+  if (!x || !weight || !out || n_rows <= 0 || dim <= 0) return SDV2_ERR_INVALID_ARG;
+  if (dim % 8 || dim > sdv2::kRowThreads * sdv2::kMaxVecPerThread * 8) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  if (!a16(x) || !a16(weight) || !a16(out) || x_row_stride % 8 || out_row_stride % 8) return SDV2_ERR_MISALIGNED;
+  if (n_rows > 0x7FFFFFFFLL) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  sdv2::RowParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.x_stride = x_row_stride;
+  p.out_stride = out_row_stride;
+  p.n_rows = n_rows;
+  p.dim = dim;
+  p.eps = eps;
+  p.w = static_cast<const __nv_bfloat16*>(weight);
+  sdv2::row_norm_kernel<false><<<static_cast<unsigned>(n_rows), sdv2::kRowThreads, 0,
+                                 static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
+}
+
+extern "C" int sdv2_ln_modulate(const void* x, const void* scale1p, const void* shift, void* out, int batch,
+                                int frames, int tokens_per_frame, int dim, float eps, void* stream) {
+  if (!x || !scale1p || !shift || !out || batch <= 0 || frames <= 0 || tokens_per_frame <= 0 || dim <= 0)
+    return SDV2_ERR_INVALID_ARG;
+  if (dim % 8 || dim > sdv2::kRowThreads * sdv2::kMaxVecPerThread * 8) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  if (!a16(x) || !a16(scale1p) || !a16(shift) || !a16(out)) return SDV2_ERR_MISALIGNED;
+  const int64_t n_rows = static_cast<int64_t>(batch) * frames * tokens_per_frame;
+  if (n_rows > 0x7FFFFFFFLL) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  sdv2::RowParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.x_stride = p.out_stride = dim;
+  p.n_rows = n_rows;
+  p.dim = dim;
+  p.eps = eps;
+  p.scale1p = static_cast<const __nv_bfloat16*>(scale1p);
+  p.shift = static_cast<const __nv_bfloat16*>(shift);
+  p.frames = frames;
+  p.tokens_per_frame = tokens_per_frame;
+  p.tokens_per_batch = frames * tokens_per_frame;
+  sdv2::row_norm_kernel<true><<<static_cast<unsigned>(n_rows), sdv2::kRowThreads, 0,
+                                static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
+}
+
+extern "C" int sdv2_gate_residual(const void* x, const void* y, const void* gate, void* out, int batch, int frames,
+                                  int tokens_per_frame, int dim, void* stream) {
+  if (!x || !y || !gate || !out || batch <= 0 || frames <= 0 || tokens_per_frame <= 0 || dim <= 0)
+    return SDV2_ERR_INVALID_ARG;
+  if (dim % 8) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  if (!a16(x) || !a16(y) || !a16(gate) || !a16(out)) return SDV2_ERR_MISALIGNED;
+  sdv2::GateParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.y = static_cast<const __nv_bfloat16*>(y);
+  p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.n_rows = static_cast<int64_t>(batch) * frames * tokens_per_frame;
+  p.dim = dim;
+  p.frames = frames;
+  p.tokens_per_frame = tokens_per_frame;
+  p.tokens_per_batch = frames * tokens_per_frame;
+  const int64_t total = p.n_rows * (dim >> 3);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  sdv2::gate_residual_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
+}

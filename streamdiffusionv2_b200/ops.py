@@ -177,6 +177,45 @@ def attn_kvcache_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     return out
 
 
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMS norm over the last dimension of a bf16 tensor whose rows are contiguous runs of `dim`
+    (rows themselves may be strided, e.g. a slice of a fused projection)."""
+    dim = x.shape[-1]
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    x2 = x.reshape(-1, dim) if x.is_contiguous() else x.flatten(0, -2)
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    with _Logged("rmsnorm", 2.0 * x.numel() * 2):
+        rc = N.lib().sdv2_rmsnorm(x2.data_ptr(), x2.stride(0), weight.data_ptr(), out.data_ptr(), dim,
+                                  x2.shape[0], dim, eps, N.stream_ptr(x.device))
+    N.check(rc, "sdv2_rmsnorm")
+    return out
+
+
+def ln_modulate(x: torch.Tensor, scale1p: torch.Tensor, shift: torch.Tensor, frames: int, eps: float) -> torch.Tensor:
+    """bf16(bf16(bf16(LN(x)) * scale1p) + shift) with per-frame scale1p / shift [B, frames, dim]."""
+    B, L, dim = x.shape
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    with _Logged("ln_modulate", 2.0 * x.numel() * 2):
+        rc = N.lib().sdv2_ln_modulate(x.data_ptr(), scale1p.contiguous().data_ptr(), shift.contiguous().data_ptr(),
+                                      out.data_ptr(), B, frames, L // frames, dim, eps, N.stream_ptr(x.device))
+    N.check(rc, "sdv2_ln_modulate")
+    return out
+
+
+def gate_residual(x: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, frames: int) -> torch.Tensor:
+    """bf16(x + bf16(y * gate)) with per-frame gate [B, frames, dim]."""
+    B, L, dim = x.shape
+    x, y = x.contiguous(), y.contiguous()
+    out = torch.empty_like(x)
+    with _Logged("gate_residual", 3.0 * x.numel() * 2):
+        rc = N.lib().sdv2_gate_residual(x.data_ptr(), y.data_ptr(), gate.contiguous().data_ptr(), out.data_ptr(), B,
+                                        frames, L // frames, dim, N.stream_ptr(x.device))
+    N.check(rc, "sdv2_gate_residual")
+    return out
+
+
 def read_status(device: torch.device) -> None:
     """Synchronise the current stream and raise if a device-side wait ran out since the last call."""
     ws = workspace(device)

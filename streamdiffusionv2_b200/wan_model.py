@@ -20,6 +20,13 @@ import torch
 import torch.nn as nn
 
 from . import causal_attention as CA
+from . import ops
+
+
+def _fusable(x: torch.Tensor) -> bool:
+    """The fused element-wise kernels serve bf16 CUDA tensors; anything else (the fp32 CPU runs
+    of the tests) takes the PyTorch op chain they reproduce."""
+    return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192
 
 
 def timestep_features(dim: int, t: torch.Tensor) -> torch.Tensor:
@@ -51,6 +58,8 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
 
     def forward(self, x):
+        if _fusable(x) and self.weight.dtype == torch.bfloat16:
+            return ops.rmsnorm(x, self.weight, self.eps)       # one launch, same roundings
         xf = x.float()
         return (xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + self.eps)).type_as(x) * self.weight
 
@@ -115,18 +124,24 @@ class DiTBlock(nn.Module):
         per_frame = x.shape[1] // frames
         shift_a, scale_a, gate_a, shift_f, scale_f, gate_f = (self.modulation.unsqueeze(1) + e).chunk(6, dim=2)
 
-        def modulate(y, scale, shift):
-            return (y.unflatten(1, (frames, per_frame)) * (1 + scale) + shift).flatten(1, 2)
+        fused = _fusable(x) and shift_a.dtype == torch.bfloat16
 
-        def gated(y, gate):
-            return (y.unflatten(1, (frames, per_frame)) * gate).flatten(1, 2)
+        def norm_modulate(norm, y, scale, shift):
+            if fused:
+                return ops.ln_modulate(y, (1 + scale).squeeze(2), shift.squeeze(2), frames, norm.eps)
+            return (norm(y).unflatten(1, (frames, per_frame)) * (1 + scale) + shift).flatten(1, 2)
 
-        y = self.self_attn(modulate(self.norm1(x), scale_a, shift_a), None, grid_sizes, freqs, None,
+        def add_gated(x, y, gate):
+            if fused:
+                return ops.gate_residual(x, y, gate.squeeze(2), frames)
+            return x + (y.unflatten(1, (frames, per_frame)) * gate).flatten(1, 2)
+
+        y = self.self_attn(norm_modulate(self.norm1, x, scale_a, shift_a), None, grid_sizes, freqs, None,
                            kv_cache, current_start, None)
-        x = x + gated(y, gate_a)
+        x = add_gated(x, y, gate_a)
         x = x + self.cross_attn(self.norm3(x), context, None, crossattn_cache=crossattn_cache)
-        y = self.ffn(modulate(self.norm2(x), scale_f, shift_f))
-        return x + gated(y, gate_f)
+        y = self.ffn(norm_modulate(self.norm2, x, scale_f, shift_f))
+        return add_gated(x, y, gate_f)
 
 
 class OutputHead(nn.Module):

@@ -266,3 +266,40 @@ def test_attention_full_size_tensor_core_vs_cuda_core():
     ref = orc.attend_explicit(q[:, rows], k, v, [S], dtype=torch.float32)
     e2 = (out[:, rows].float().cpu() - ref).abs()
     assert e2.max().item() <= TOL_MAX and e2.mean().item() <= TOL_MEAN
+
+
+def test_fused_block_elementwise_match_their_op_chains():
+    """rmsnorm / ln_modulate / gate_residual against the PyTorch op chains they replace, on the
+    GPU in bf16: identical up to isolated single-bf16-step differences (reduction order)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(11)
+    B, F, fs, dim = 2, 2, 1560, 1536
+    L = F * fs
+    x = (torch.randn(B, L, dim, generator=g) * 2).to(torch.bfloat16).cuda()
+    y = torch.randn(B, L, dim, generator=g).to(torch.bfloat16).cuda()
+    w = (1 + 0.1 * torch.randn(dim, generator=g)).to(torch.bfloat16).cuda()
+    mod = (0.3 * torch.randn(B, F, 3, dim, generator=g)).to(torch.bfloat16).cuda()
+    scale, shift, gate = mod.chunk(3, dim=2)
+
+    def close(a, b):
+        d = (a.float() - b.float()).abs()
+        step = b.float().abs().clamp_min(2.0 ** -120) * 2.0 ** -7     # one bf16 step at that magnitude
+        assert (d <= step).all(), d.max().item()
+        assert (a == b).float().mean().item() > 0.995
+
+    xf = x.float()
+    want = (xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + 1e-6)).type_as(x) * w
+    close(ops.rmsnorm(x, w, 1e-6), want)
+    # a strided slice of a wider projection
+    wide = torch.randn(B, L, 3 * dim, generator=g).to(torch.bfloat16).cuda()
+    sl = wide[..., dim:2 * dim]
+    sf = sl.float()
+    close(ops.rmsnorm(sl, w, 1e-6), (sf * torch.rsqrt(sf.pow(2).mean(dim=-1, keepdim=True) + 1e-6)).type_as(sl) * w)
+
+    ln = torch.nn.functional.layer_norm(x, (dim,), eps=1e-6)
+    want = (ln.unflatten(1, (F, fs)) * (1 + scale) + shift).flatten(1, 2)
+    close(ops.ln_modulate(x, (1 + scale).squeeze(2), shift.squeeze(2), F, 1e-6), want)
+
+    want = x + (y.unflatten(1, (F, fs)) * gate).flatten(1, 2)
+    got = ops.gate_residual(x, y, gate.squeeze(2), F)
+    assert torch.equal(got, want)
