@@ -21,7 +21,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from .stage_transport import StageLink, StagePacket, contiguous_block_ranges
-from .stream_pipeline import StreamPipeline
+from .stream_pipeline import StreamPipeline, assign_ints
 
 
 class PipelineStageRunner:
@@ -58,8 +58,8 @@ class PipelineStageRunner:
                     if not last:
                         link.post_recv()
                 pipe.hidden_states.copy_(back.latents)
-                pipe.kv_cache_starts.copy_(torch.tensor(back.starts, dtype=torch.long), non_blocking=True)
-                pipe.kv_cache_ends.copy_(torch.tensor(back.ends, dtype=torch.long), non_blocking=True)
+                assign_ints(pipe.kv_cache_starts, back.starts)
+                assign_ints(pipe.kv_cache_ends, back.ends)
                 pipe._starts_host = list(back.starts)
                 pipe._ends_host = list(back.ends)
             elif self.items == self.world - 1 and not last:

@@ -21,6 +21,13 @@ import torch.nn as nn
 from .causal_attention import HostStarts
 
 
+def assign_ints(t: torch.Tensor, values) -> None:
+    """t[j] = values[j] with device-side fills.  A copy from pageable host memory would make the
+    stream wait for all earlier work before it starts, i.e. synchronise the host with the GPU."""
+    for j, v in enumerate(values):
+        t[j:j + 1].fill_(int(v))       # `t[j] = v` goes through a host scalar tensor and synchronises
+
+
 class FlowSchedule:
     """Shifted linear sigma table; timesteps = sigma * 1000 (flow_match.py:7-45, with
     extra_one_step=True, sigma_min=0, as the wrapper configures it, wan_wrapper.py:164-167)."""
@@ -237,16 +244,17 @@ class StreamPipeline(nn.Module):
         self.hidden_states[1:] = self.hidden_states[:-1].clone()
         self.hidden_states[0] = noise[0]
         self.kv_cache_starts[1:] = self.kv_cache_starts[:-1].clone()
-        self.kv_cache_starts[0] = current_start
+        self.kv_cache_starts[0:1].fill_(int(current_start))
         self.kv_cache_ends[1:] = self.kv_cache_ends[:-1].clone()
-        self.kv_cache_ends[0] = current_end
+        self.kv_cache_ends[0:1].fill_(int(current_end))
         self._starts_host = [int(current_start)] + self._starts_host[:-1]
         self._ends_host = [int(current_end)] + self._ends_host[:-1]
 
     def _renoise(self, x):
         for i in range(len(self.denoising_step_list) - 1):
-            x[[i]] = self.scheduler.add_noise(
-                x[[i]], torch.randn_like(x[[i]]),
+            row = x[i:i + 1]          # slices, not list indices: an index list is copied host->device
+            x[i:i + 1] = self.scheduler.add_noise(
+                row, torch.randn_like(row),
                 self.denoising_step_list[i + 1] * torch.ones([1], device=x.device, dtype=torch.long))
         return x
 
@@ -297,17 +305,19 @@ class StreamPipeline(nn.Module):
         else:
             self.block_x.copy_(block_x)
             self.hidden_states.copy_(noise)
-            if not isinstance(current_start, torch.Tensor):   # host lists: no read-back needed
-                starts_host = current_start
-                current_start = torch.tensor(list(current_start), dtype=torch.long)
-            if not isinstance(current_end, torch.Tensor):
-                self._ends_host = [int(v) for v in current_end]
-                current_end = torch.tensor(list(current_end), dtype=torch.long)
-            else:
+            if isinstance(current_start, torch.Tensor):
+                self.kv_cache_starts.copy_(current_start)
+                self._starts_host = [int(v) for v in (starts_host if starts_host is not None
+                                                      else current_start.tolist())]
+            else:                                             # host lists: no read-back, no host->device copy
+                self._starts_host = [int(v) for v in current_start]
+                assign_ints(self.kv_cache_starts, self._starts_host)
+            if isinstance(current_end, torch.Tensor):
+                self.kv_cache_ends.copy_(current_end)
                 self._ends_host = [int(v) for v in current_end.tolist()]
-            self.kv_cache_starts.copy_(current_start, non_blocking=True)
-            self.kv_cache_ends.copy_(current_end, non_blocking=True)
-            self._starts_host = [int(v) for v in (starts_host if starts_host is not None else current_start.tolist())]
+            else:
+                self._ends_host = [int(v) for v in current_end]
+                assign_ints(self.kv_cache_ends, self._ends_host)
         if current_step is not None:
             self.timestep[0] = current_step
         common = dict(conditional_dict=self.conditional_dict,

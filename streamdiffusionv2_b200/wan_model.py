@@ -194,6 +194,7 @@ class CausalWanModel(nn.Module):
         self.freqs = build_rope_table(head_dim)
         self.num_frame_per_block = 1
         self.last_patched_x_shape = None
+        self._shape_tensors = {}
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -234,7 +235,11 @@ class CausalWanModel(nn.Module):
             x = self.patch_embedding(x if isinstance(x, torch.Tensor) else torch.stack(list(x)))
             bsz, cch, frames, gh, gw = x.shape
             self.last_patched_x_shape = [1, int(cch), int(frames), int(gh), int(gw)]   # host copy for stage links
-            patched_x_shape = torch.tensor(self.last_patched_x_shape, dtype=torch.int64, device=device)
+            key = (tuple(self.last_patched_x_shape), str(device))
+            patched_x_shape = self._shape_tensors.get(key)       # built once: a host->device copy synchronises
+            if patched_x_shape is None:
+                patched_x_shape = torch.tensor(self.last_patched_x_shape, dtype=torch.int64, device=device)
+                self._shape_tensors[key] = patched_x_shape
             x = x.flatten(2).transpose(1, 2)
         else:
             _, cch, frames, gh, gw = _as_ints(patched_x_shape)

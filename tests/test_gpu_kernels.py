@@ -281,24 +281,30 @@ def test_fused_block_elementwise_match_their_op_chains():
     mod = (0.3 * torch.randn(B, F, 3, dim, generator=g)).to(torch.bfloat16).cuda()
     scale, shift, gate = mod.chunk(3, dim=2)
 
-    def close(a, b):
+    def close(a, b, what, scale_ref=None):
+        # two chained bf16 roundings: a last-bit difference in the statistics can move the result
+        # by up to two bf16 steps (of the largest intermediate) on isolated elements; almost all
+        # elements are identical
         d = (a.float() - b.float()).abs()
-        step = b.float().abs().clamp_min(2.0 ** -120) * 2.0 ** -7     # one bf16 step at that magnitude
-        assert (d <= step).all(), d.max().item()
-        assert (a == b).float().mean().item() > 0.995
+        mag = b.float().abs() if scale_ref is None else torch.maximum(b.float().abs(), scale_ref.float().abs())
+        step = mag.clamp_min(2.0 ** -120) * 2.0 ** -6
+        assert (d <= step).all(), (what, d.max().item())
+        assert (a == b).float().mean().item() > 0.995, what
 
     xf = x.float()
     want = (xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + 1e-6)).type_as(x) * w
-    close(ops.rmsnorm(x, w, 1e-6), want)
+    close(ops.rmsnorm(x, w, 1e-6), want, 'rmsnorm')
     # a strided slice of a wider projection
     wide = torch.randn(B, L, 3 * dim, generator=g).to(torch.bfloat16).cuda()
     sl = wide[..., dim:2 * dim]
     sf = sl.float()
-    close(ops.rmsnorm(sl, w, 1e-6), (sf * torch.rsqrt(sf.pow(2).mean(dim=-1, keepdim=True) + 1e-6)).type_as(sl) * w)
+    close(ops.rmsnorm(sl, w, 1e-6), (sf * torch.rsqrt(sf.pow(2).mean(dim=-1, keepdim=True) + 1e-6)).type_as(sl) * w,
+          'rmsnorm strided')
 
     ln = torch.nn.functional.layer_norm(x, (dim,), eps=1e-6)
     want = (ln.unflatten(1, (F, fs)) * (1 + scale) + shift).flatten(1, 2)
-    close(ops.ln_modulate(x, (1 + scale).squeeze(2), shift.squeeze(2), F, 1e-6), want)
+    close(ops.ln_modulate(x, (1 + scale).squeeze(2), shift.squeeze(2), F, 1e-6), want, 'ln_modulate',
+          scale_ref=(ln.unflatten(1, (F, fs)) * (1 + scale)).flatten(1, 2))
 
     want = x + (y.unflatten(1, (F, fs)) * gate).flatten(1, 2)
     got = ops.gate_residual(x, y, gate.squeeze(2), F)
