@@ -167,19 +167,21 @@ int sdv2_attn_kvcache_static(const sdv2_view* q, const sdv2_view* k_cache, const
  * sdv2_rmsnorm: out[r,:] = bf16(bf16(x[r,:] * rsqrt(mean(x[r,:]^2) + eps)) * weight) - WanRMSNorm.forward
  *   (models/wan/wan_base/modules/model.py:70-86) applied to the q / k projections
  *   (models/wan/causal_model.py:212-214).  Row strides in elements (a slice of a fused projection is fine).
- * sdv2_ln_modulate: out = bf16(bf16(bf16(LayerNorm(x)) * scale1p[b,f]) + shift[b,f]) for x [batch,
- *   frames * tokens_per_frame, dim], scale1p = 1 + scale and shift [batch, frames, dim] - the adaLN
- *   modulation in front of self-attention and the FFN (models/wan/causal_model.py:463-467, 477-480).
+ * sdv2_ln_modulate: out = bf16(bf16(bf16(LayerNorm(x)) * bf16(1 + scale[b,f])) + shift[b,f]) for x [batch,
+ *   frames * tokens_per_frame, dim] - the adaLN modulation in front of self-attention and the FFN
+ *   (models/wan/causal_model.py:463-467, 477-480).  scale / shift point at the first row of their
+ *   chunk of the [batch, frames, 6, dim] modulation tensor; row (b * frames + f) starts
+ *   mod_row_stride elements after the previous one (6 * dim in place, dim if copied out).
  * sdv2_gate_residual: out = bf16(x + bf16(y * gate[b,f])) - the gated residual after them
- *   (models/wan/causal_model.py:470-471, 482-483).  out may alias x.
+ *   (models/wan/causal_model.py:470-471, 482-483); gate addressed like scale.  out may alias x.
  * dim must be a multiple of 8 and at most 8192; all pointers 16-byte aligned.
  */
 int sdv2_rmsnorm(const void* x, int64_t x_row_stride, const void* weight, void* out, int64_t out_row_stride,
                  int64_t n_rows, int dim, float eps, void* stream);
-int sdv2_ln_modulate(const void* x, const void* scale1p, const void* shift, void* out, int batch, int frames,
-                     int tokens_per_frame, int dim, float eps, void* stream);
-int sdv2_gate_residual(const void* x, const void* y, const void* gate, void* out, int batch, int frames,
-                       int tokens_per_frame, int dim, void* stream);
+int sdv2_ln_modulate(const void* x, const void* scale, const void* shift, int64_t mod_row_stride, void* out,
+                     int batch, int frames, int tokens_per_frame, int dim, float eps, void* stream);
+int sdv2_gate_residual(const void* x, const void* y, const void* gate, int64_t mod_row_stride, void* out, int batch,
+                       int frames, int tokens_per_frame, int dim, void* stream);
 
 /* Synchronises `stream`, reads the status word at the start of a workspace and clears it.
  * Returns SDV2_OK, SDV2_ERR_TIMEOUT (a device-side wait ran out; *detail = where) or

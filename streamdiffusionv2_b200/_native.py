@@ -53,8 +53,10 @@ _SIGNATURES = {
                                                                     C.POINTER(C.c_void_p), C.c_void_p]),
     "sdv2_rmsnorm": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int,
                                C.c_float, C.c_void_p]),
-    "sdv2_ln_modulate": (C.c_int, [C.c_void_p] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p]),
-    "sdv2_gate_residual": (C.c_int, [C.c_void_p] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "sdv2_ln_modulate": (C.c_int, [C.c_void_p] * 3 + [C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                      C.c_float, C.c_void_p]),
+    "sdv2_gate_residual": (C.c_int, [C.c_void_p] * 3 + [C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                        C.c_void_p]),
     "sdv2_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.c_void_p]),
     "sdv2_selftest_umma": (C.c_int, [C.c_void_p] * 4 + [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }

@@ -4,7 +4,7 @@
 // to the cache kernels are the ones the unfused chain would produce.
 //
 //   rmsnorm        : bf16( bf16(x * rsqrt(mean(x^2) + eps)) * w )                     per token row
-//   ln_modulate    : bf16( bf16( bf16(LN(x)) * scale1p[b, frame] ) + shift[b, frame] )  per token row
+//   ln_modulate    : bf16( bf16( bf16(LN(x)) * bf16(1 + scale[b, frame]) ) + shift[b, frame] )  per token row
 //   gate_residual  : bf16( x + bf16(y * gate[b, frame]) )                              per element
 //
 // All three are pure streaming kernels (one read and one write of [tokens, dim], plus y for the
@@ -47,8 +47,9 @@ struct RowParams {
   int dim;
   float eps;
   const __nv_bfloat16* w;        // rmsnorm weight [dim]
-  const __nv_bfloat16* scale1p;  // ln_modulate: (1 + scale) [batch, frames, dim]
-  const __nv_bfloat16* shift;    // ln_modulate: shift [batch, frames, dim]
+  const __nv_bfloat16* scale1p;  // ln_modulate: scale, row (b * frames + f) at mod_stride elements
+  const __nv_bfloat16* shift;    // ln_modulate: shift, same addressing
+  int64_t mod_stride;
   int tokens_per_batch, tokens_per_frame, frames;
 };
 
@@ -100,7 +101,7 @@ __global__ void __launch_bounds__(kRowThreads) row_norm_kernel(const __grid_cons
   if (kLayerNorm) {
     const int64_t b = row / p.tokens_per_batch;
     const int f = static_cast<int>((row - b * p.tokens_per_batch) / p.tokens_per_frame);
-    const int64_t off = (b * p.frames + f) * p.dim;
+    const int64_t off = (b * p.frames + f) * p.mod_stride;
     mul = reinterpret_cast<const uint4*>(p.scale1p + off);
     add = reinterpret_cast<const uint4*>(p.shift + off);
   } else {
@@ -124,8 +125,10 @@ __global__ void __launch_bounds__(kRowThreads) row_norm_kernel(const __grid_cons
       for (int j = 0; j < 4; ++j) {
         float lo = bf16_round((lo_f(w[j]) - mean) * rstd);
         float hi = bf16_round((hi_f(w[j]) - mean) * rstd);
-        lo = lo * lo_f(m[j]);
-        hi = hi * hi_f(m[j]);
+        const float ml = kLayerNorm ? bf16_round(1.f + lo_f(m[j])) : lo_f(m[j]);   // (1 + scale) is a bf16 op upstream
+        const float mh = kLayerNorm ? bf16_round(1.f + hi_f(m[j])) : hi_f(m[j]);
+        lo = lo * ml;
+        hi = hi * mh;
         if (kLayerNorm) {
           lo = bf16_round(lo) + lo_f(a4[j]);
           hi = bf16_round(hi) + hi_f(a4[j]);
@@ -140,9 +143,9 @@ __global__ void __launch_bounds__(kRowThreads) row_norm_kernel(const __grid_cons
 struct GateParams {
   const __nv_bfloat16* x;
   const __nv_bfloat16* y;
-  const __nv_bfloat16* gate;  // [batch, frames, dim]
+  const __nv_bfloat16* gate;  // row (b * frames + f) at mod_stride elements
   __nv_bfloat16* out;
-  int64_t n_rows;
+  int64_t n_rows, mod_stride;
   int dim, tokens_per_batch, tokens_per_frame, frames;
 };
 
@@ -157,7 +160,7 @@ __global__ void __launch_bounds__(256) gate_residual_kernel(const __grid_constan
     const int f = static_cast<int>((row - b * p.tokens_per_batch) / p.tokens_per_frame);
     const uint4 xv = reinterpret_cast<const uint4*>(p.x)[i];
     const uint4 yv = reinterpret_cast<const uint4*>(p.y)[i];
-    const uint4 gv = __ldg(reinterpret_cast<const uint4*>(p.gate + (b * p.frames + f) * p.dim) + c);
+    const uint4 gv = __ldg(reinterpret_cast<const uint4*>(p.gate + (b * p.frames + f) * p.mod_stride) + c);
     const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, yw[4] = {yv.x, yv.y, yv.z, yv.w},
                    gw[4] = {gv.x, gv.y, gv.z, gv.w};
     uint32_t o[4];
@@ -197,10 +200,12 @@ extern "C" int sdv2_rmsnorm(const void* x, int64_t x_row_stride, const void* wei
   return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
 }
 
-extern "C" int sdv2_ln_modulate(const void* x, const void* scale1p, const void* shift, void* out, int batch,
-                                int frames, int tokens_per_frame, int dim, float eps, void* stream) {
+extern "C" int sdv2_ln_modulate(const void* x, const void* scale1p, const void* shift, int64_t mod_row_stride,
+                                void* out, int batch, int frames, int tokens_per_frame, int dim, float eps,
+                                void* stream) {
   if (!x || !scale1p || !shift || !out || batch <= 0 || frames <= 0 || tokens_per_frame <= 0 || dim <= 0)
     return SDV2_ERR_INVALID_ARG;
+  if (mod_row_stride < dim || mod_row_stride % 8) return SDV2_ERR_MISALIGNED;
   if (dim % 8 || dim > sdv2::kRowThreads * sdv2::kMaxVecPerThread * 8) return SDV2_ERR_UNSUPPORTED_SHAPE;
   if (!a16(x) || !a16(scale1p) || !a16(shift) || !a16(out)) return SDV2_ERR_MISALIGNED;
   const int64_t n_rows = static_cast<int64_t>(batch) * frames * tokens_per_frame;
@@ -214,6 +219,7 @@ extern "C" int sdv2_ln_modulate(const void* x, const void* scale1p, const void* 
   p.eps = eps;
   p.scale1p = static_cast<const __nv_bfloat16*>(scale1p);
   p.shift = static_cast<const __nv_bfloat16*>(shift);
+  p.mod_stride = mod_row_stride;
   p.frames = frames;
   p.tokens_per_frame = tokens_per_frame;
   p.tokens_per_batch = frames * tokens_per_frame;
@@ -222,10 +228,11 @@ extern "C" int sdv2_ln_modulate(const void* x, const void* scale1p, const void* 
   return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
 }
 
-extern "C" int sdv2_gate_residual(const void* x, const void* y, const void* gate, void* out, int batch, int frames,
-                                  int tokens_per_frame, int dim, void* stream) {
+extern "C" int sdv2_gate_residual(const void* x, const void* y, const void* gate, int64_t mod_row_stride, void* out,
+                                  int batch, int frames, int tokens_per_frame, int dim, void* stream) {
   if (!x || !y || !gate || !out || batch <= 0 || frames <= 0 || tokens_per_frame <= 0 || dim <= 0)
     return SDV2_ERR_INVALID_ARG;
+  if (mod_row_stride < dim || mod_row_stride % 8) return SDV2_ERR_MISALIGNED;
   if (dim % 8) return SDV2_ERR_UNSUPPORTED_SHAPE;
   if (!a16(x) || !a16(y) || !a16(gate) || !a16(out)) return SDV2_ERR_MISALIGNED;
   sdv2::GateParams p = {};
@@ -234,6 +241,7 @@ extern "C" int sdv2_gate_residual(const void* x, const void* y, const void* gate
   p.gate = static_cast<const __nv_bfloat16*>(gate);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.n_rows = static_cast<int64_t>(batch) * frames * tokens_per_frame;
+  p.mod_stride = mod_row_stride;
   p.dim = dim;
   p.frames = frames;
   p.tokens_per_frame = tokens_per_frame;

@@ -192,26 +192,42 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return out
 
 
-def ln_modulate(x: torch.Tensor, scale1p: torch.Tensor, shift: torch.Tensor, frames: int, eps: float) -> torch.Tensor:
-    """bf16(bf16(bf16(LN(x)) * scale1p) + shift) with per-frame scale1p / shift [B, frames, dim]."""
+def _mod_rows(t: torch.Tensor, B: int, frames: int, dim: int):
+    """(pointer, row stride) of a [B, frames, (1,) dim] chunk of the modulation tensor, in place
+    when rows are evenly spaced (a chunk of [B, frames, 6, dim] is), else through a copy."""
+    t = t.reshape(B, frames, dim) if t.is_contiguous() else t.squeeze(2) if t.dim() == 4 else t
+    if t.stride(-1) == 1 and (B == 1 or t.stride(0) == frames * t.stride(1)) and t.stride(1) % 8 == 0:
+        return t, t.stride(1)
+    t = t.contiguous()
+    return t, dim
+
+
+def ln_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, frames: int, eps: float) -> torch.Tensor:
+    """bf16(bf16(bf16(LN(x)) * bf16(1 + scale)) + shift) with per-frame scale / shift
+    [B, frames, (1,) dim], read in place from the modulation tensor."""
     B, L, dim = x.shape
     x = x.contiguous()
     out = torch.empty_like(x)
+    sc, stride = _mod_rows(scale, B, frames, dim)
+    sh, stride2 = _mod_rows(shift, B, frames, dim)
+    if stride2 != stride:
+        sc, sh, stride = sc.contiguous(), sh.contiguous(), dim
     with _Logged("ln_modulate", 2.0 * x.numel() * 2):
-        rc = N.lib().sdv2_ln_modulate(x.data_ptr(), scale1p.contiguous().data_ptr(), shift.contiguous().data_ptr(),
-                                      out.data_ptr(), B, frames, L // frames, dim, eps, N.stream_ptr(x.device))
+        rc = N.lib().sdv2_ln_modulate(x.data_ptr(), sc.data_ptr(), sh.data_ptr(), stride, out.data_ptr(), B, frames,
+                                      L // frames, dim, eps, N.stream_ptr(x.device))
     N.check(rc, "sdv2_ln_modulate")
     return out
 
 
 def gate_residual(x: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, frames: int) -> torch.Tensor:
-    """bf16(x + bf16(y * gate)) with per-frame gate [B, frames, dim]."""
+    """bf16(x + bf16(y * gate)) with per-frame gate [B, frames, (1,) dim] read in place."""
     B, L, dim = x.shape
     x, y = x.contiguous(), y.contiguous()
     out = torch.empty_like(x)
+    gt, stride = _mod_rows(gate, B, frames, dim)
     with _Logged("gate_residual", 3.0 * x.numel() * 2):
-        rc = N.lib().sdv2_gate_residual(x.data_ptr(), y.data_ptr(), gate.contiguous().data_ptr(), out.data_ptr(), B,
-                                        frames, L // frames, dim, N.stream_ptr(x.device))
+        rc = N.lib().sdv2_gate_residual(x.data_ptr(), y.data_ptr(), gt.data_ptr(), stride, out.data_ptr(), B, frames,
+                                        L // frames, dim, N.stream_ptr(x.device))
     N.check(rc, "sdv2_gate_residual")
     return out
 

@@ -128,12 +128,12 @@ class DiTBlock(nn.Module):
 
         def norm_modulate(norm, y, scale, shift):
             if fused:
-                return ops.ln_modulate(y, (1 + scale).squeeze(2), shift.squeeze(2), frames, norm.eps)
+                return ops.ln_modulate(y, scale, shift, frames, norm.eps)
             return (norm(y).unflatten(1, (frames, per_frame)) * (1 + scale) + shift).flatten(1, 2)
 
         def add_gated(x, y, gate):
             if fused:
-                return ops.gate_residual(x, y, gate.squeeze(2), frames)
+                return ops.gate_residual(x, y, gate, frames)
             return x + (y.unflatten(1, (frames, per_frame)) * gate).flatten(1, 2)
 
         y = self.self_attn(norm_modulate(self.norm1, x, scale_a, shift_a), None, grid_sizes, freqs, None,

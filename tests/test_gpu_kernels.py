@@ -303,9 +303,9 @@ def test_fused_block_elementwise_match_their_op_chains():
 
     ln = torch.nn.functional.layer_norm(x, (dim,), eps=1e-6)
     want = (ln.unflatten(1, (F, fs)) * (1 + scale) + shift).flatten(1, 2)
-    close(ops.ln_modulate(x, (1 + scale).squeeze(2), shift.squeeze(2), F, 1e-6), want, 'ln_modulate',
+    close(ops.ln_modulate(x, scale, shift, F, 1e-6), want, 'ln_modulate',
           scale_ref=(ln.unflatten(1, (F, fs)) * (1 + scale)).flatten(1, 2))
 
     want = x + (y.unflatten(1, (F, fs)) * gate).flatten(1, 2)
-    got = ops.gate_residual(x, y, gate.squeeze(2), F)
+    got = ops.gate_residual(x, y, gate, F)
     assert torch.equal(got, want)
