@@ -351,7 +351,7 @@ def run_pipeline(args):
                      owned_blocks=range(ranges[rank][0], ranges[rank][1]), unowned="free")
         link = StageLink(rank, world, device, (rows, n_tok, MODEL_1P3B["dim"]),
                          (rows, FRAMES_PER_CHUNK, 16, h, w), dtype=torch.bfloat16, timeout_s=90)
-        runner = PipelineStageRunner(pipe, link, rank, world, ranges)
+        runner = PipelineStageRunner(pipe, link, rank, world, ranges, prefetch=bool(int(os.environ.get("SDV2_PREFETCH", "0"))))
         chunk = [0]
 
         def one_step(src, last=False):
@@ -383,6 +383,7 @@ def run_pipeline(args):
             sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
+        runner.stage_events = []
         e0.record()
         phase(args.steps, resident)                       # ring starts empty and ends empty
         e1.record()
@@ -390,6 +391,8 @@ def run_pipeline(args):
         clocks = sampler.stop() if rank == 0 else None
         ops.set_launch_log(None)
         ms = e0.elapsed_time(e1)
+        stage_ms = statistics.mean(a.elapsed_time(b) for a, b in runner.stage_events)
+        runner.stage_events = None
 
         e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -406,6 +409,8 @@ def run_pipeline(args):
                          dtype=torch.float64, device=device)
     mx = stats.clone()
     dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    per_stage = [torch.zeros(1, dtype=torch.float64, device=device) for _ in range(world)]
+    dist.all_gather(per_stage, torch.tensor([stage_ms], dtype=torch.float64, device=device))
     sm = stats.clone()
     dist.all_reduce(sm, op=dist.ReduceOp.SUM)
     if rank == 0:
@@ -427,7 +432,7 @@ def run_pipeline(args):
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
                          "traffic": None, "avg_launch_ms": att_ms, "flops_per_launch": att_flops},
             "cpu_baseline": None, "clocks": clocks,
-            "stage_blocks": ranges, "stage_hop_bytes": rows * n_tok * MODEL_1P3B["dim"] * 2,
+            "stage_blocks": ranges, "stage_compute_ms": [round(t.item(), 3) for t in per_stage], "stage_hop_bytes": rows * n_tok * MODEL_1P3B["dim"] * 2,
         }
         print(json.dumps(line))
     dist.destroy_process_group()

@@ -26,7 +26,11 @@ from .stream_pipeline import StreamPipeline, assign_ints
 
 class PipelineStageRunner:
     def __init__(self, pipe: StreamPipeline, link: StageLink, rank: int, world_size: int,
-                 block_ranges: Optional[Sequence[Sequence[int]]] = None):
+                 block_ranges: Optional[Sequence[Sequence[int]]] = None, prefetch: bool = False):
+        # prefetch: post the next receive one chunk ahead.  Off by default: a posted NCCL receive is a
+        # kernel that spins on a few SMs until its data arrives, and the attention CTAs (which need a
+        # whole SM's shared memory) cannot run on those SMs meanwhile; a 20 MB hop takes ~30 us anyway.
+        self.prefetch = prefetch
         self.pipe, self.link, self.rank, self.world = pipe, link, rank, world_size
         ranges = block_ranges or contiguous_block_ranges(pipe.num_transformer_blocks, world_size)
         self.block_range = [int(ranges[rank][0]), int(ranges[rank][1])]
@@ -34,6 +38,7 @@ class PipelineStageRunner:
         self.items = 0            # chunks processed (stage 0: sent)
         self.received = 0         # stage 0: packets taken from the closing edge
         self._returned = deque()  # stage 0: packets taken in by quiesce(), not yet adopted
+        self.stage_events = None  # set to [] to record (start, end) CUDA events around each stage compute
 
     @property
     def owned_blocks(self) -> range:
@@ -55,30 +60,34 @@ class PipelineStageRunner:
                 else:
                     back = link.recv()                  # what the last stage made of chunk items-world
                     self.received += 1
-                    if not last:
+                    if self.prefetch and not last:
                         link.post_recv()
                 pipe.hidden_states.copy_(back.latents)
                 assign_ints(pipe.kv_cache_starts, back.starts)
                 assign_ints(pipe.kv_cache_ends, back.ends)
                 pipe._starts_host = list(back.starts)
                 pipe._ends_host = list(back.ends)
-            elif self.items == self.world - 1 and not last:
+            elif self.prefetch and self.items == self.world - 1 and not last:
                 link.post_recv()
+            ev = self._mark()
             act, _ = pipe.inference(noise=noise, current_start=current_start, current_end=current_end,
                                     current_step=current_step, block_mode="input", block_num=self.block_range)
+            self._mark(ev)
             link.send(chunk_idx, act, pipe.hidden_states, pipe.generator.model.last_patched_x_shape,
                       pipe._starts_host, pipe._ends_host, -1 if current_step is None else int(current_step))
             self.items += 1
             return None
 
         pkt: StagePacket = link.recv()
-        if not last:
+        if self.prefetch and not last:
             link.post_recv()
         step = None if pkt.current_step < 0 else pkt.current_step
+        ev = self._mark()
         out, pshape = pipe.inference(noise=pkt.latents, current_start=pkt.starts, current_end=pkt.ends,
                                      current_step=step, block_mode=self.role, block_num=self.block_range,
                                      patched_x_shape=pkt.patched_x_shape, block_x=pkt.activations,
                                      starts_host=pkt.starts)
+        self._mark(ev)
         if self.role == "middle":
             link.send(pkt.chunk_idx, out, pkt.latents, pkt.patched_x_shape, pkt.starts, pkt.ends, pkt.current_step)
             self.items += 1
@@ -86,6 +95,15 @@ class PipelineStageRunner:
         link.send(pkt.chunk_idx, None, out, pkt.patched_x_shape, pkt.starts, pkt.ends, pkt.current_step)
         self.items += 1
         return out
+
+    def _mark(self, start=None):
+        if self.stage_events is None:
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        if start is not None:
+            self.stage_events.append((start, e))
+        return e
 
     def quiesce(self) -> None:
         """Empty the ring: stage 0 takes in every packet still travelling back to it (they are kept

@@ -12,9 +12,12 @@ to the host before its payload can be received) with
   needs without reading device memory back.
 
 Every ring edge r -> r+1 has its own two-rank process group, hence its own communicator and
-stream: receiving chunk c+1 overlaps computing chunk c and sending chunk c-1.  Receive buffers
-are double-buffered; a receive is posted before the compute of the previous chunk is enqueued.
-The closing edge (last stage -> stage 0) carries latents only.
+stream, so a stage's send and its next receive do not serialise.  Receive buffers are
+double-buffered.  A receive may be posted one chunk ahead (`post_recv`), but the runner does not
+do so by default: a posted NCCL receive is a kernel that occupies a few SMs until its data
+arrives, and measured on B200 that slowed each stage's attention by ~20 % (its CTAs need a whole
+SM), while the 20 MB hop itself takes ~30 us.  The closing edge (last stage -> stage 0) carries
+latents only.
 
 `chunk_idx == -1` is kept as the restart sentinel of the reference drivers
 (streamv2v/inference_pipe.py:459-472).
