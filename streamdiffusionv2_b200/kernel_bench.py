@@ -80,6 +80,59 @@ def run_config(kernel, rows, heads, window_frames, chunk_frames, iters, warmup, 
     return res
 
 
+def library_baselines(rows, heads, window_frames, chunk_frames, iters, warmup):
+    """What the reference executes on a GPU for the same two steps, timed with the same protocol:
+    the fp64 complex rope chain plus the K/V slice writes (models/wan/causal_model.py:94-108,
+    321-322), and flash_attn_with_kvcache (:353-358) or, failing that, PyTorch SDPA (:111-157).
+    Library calls only - nothing here is part of the product path."""
+    import torch.nn.functional as F
+    from .wan_model import build_rope_table
+    dev = torch.device("cuda")
+    D, n, s = 128, chunk_frames * FRAME_TOKENS, window_frames * FRAME_TOKENS
+    q, k, v = (torch.randn(rows, n, heads, D, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    kc = torch.randn(rows, s, heads, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn_like(kc)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    table = build_rope_table(D).to(dev)
+    ct, ch = 64 - 2 * (64 // 3), 64 // 3
+    t, hh, ww = table.split([ct, ch, ch], dim=1)
+    mult = torch.cat([t[7:7 + chunk_frames].repeat_interleave(1560, dim=0),
+                      hh[:30].repeat_interleave(52, dim=0).repeat(chunk_frames, 1),
+                      ww[:52].repeat(30, 1).repeat(chunk_frames, 1)], dim=-1).unsqueeze(1)
+
+    def rope(x):
+        out = x.clone()
+        for i in range(rows):
+            xi = torch.view_as_complex(x[i].to(torch.float64).reshape(n, heads, -1, 2))
+            out[i] = torch.view_as_real(xi * mult).flatten(2).type_as(x)
+        return out
+
+    def chain():
+        rq, rk = rope(q), rope(k)
+        for i in range(rows):
+            kc[i:i + 1, 1560:1560 + n] = rk[i:i + 1]
+            vc[i:i + 1, 1560:1560 + n] = v[i:i + 1]
+        return rq
+
+    res = {"baseline": "library", "rows": rows, "heads": heads, "window_frames": window_frames,
+           "chunk_frames": chunk_frames}
+    med, _ = _time(chain, iters, warmup, flush)
+    res["rope_append_torch_chain_ms"] = med
+    res["rope_append_torch_chain_gbs"] = 6.0 * rows * n * heads * D * 2 / med / 1e6
+    fl = 4.0 * rows * n * s * D * heads
+    try:
+        from flash_attn import flash_attn_with_kvcache
+        lens = torch.full((rows,), s, dtype=torch.int32, device=dev)
+        med, _ = _time(lambda: flash_attn_with_kvcache(q, kc, vc, cache_seqlens=lens), iters, warmup, flush)
+        res["flash_attn_with_kvcache_ms"], res["flash_attn_with_kvcache_tflops"] = med, fl / med / 1e9
+    except Exception as e:  # not installed, or no kernel for this GPU
+        res["flash_attn_with_kvcache_error"] = repr(e)[:120]
+    qq, kk, vv = q.transpose(1, 2), kc.transpose(1, 2), vc.transpose(1, 2)
+    med, _ = _time(lambda: F.scaled_dot_product_attention(qq, kk, vv), iters, warmup, flush)
+    res["torch_sdpa_ms"], res["torch_sdpa_tflops"] = med, fl / med / 1e9
+    return res
+
+
 def check_index_run(rows, heads, window_frames, chunk_frames, steps):
     """Long wraparound run of the slot logic through the append kernel: device index tensors must
     equal the host mirror after every step, and every slot must stay inside the cache."""
@@ -132,7 +185,11 @@ def main(argv=None):
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--check-index-run", type=int, default=0)
+    ap.add_argument("--library-baselines", action="store_true")
     a = ap.parse_args(argv)
+    if a.library_baselines:
+        print(json.dumps(library_baselines(a.rows, a.heads, a.window_frames, a.chunk_frames, a.iters, a.warmup)))
+        return
     if a.check_index_run:
         print(json.dumps(check_index_run(a.rows, a.heads, a.window_frames, a.chunk_frames, a.check_index_run)))
         return
