@@ -152,7 +152,7 @@ def run_reference_arm(args):
             "cpu_baseline": {"value": fps, "unit": "video frames/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": fps, "unit": "video frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line))
+    args.emit(line)
 
 
 def metric_name():
@@ -309,7 +309,7 @@ def run_single_gpu(args):
                             "avg_launch_ms": app_ms, "bytes_per_launch": app_bytes, "traffic": None},
         "cpu_baseline": cpu, "clocks": clocks,
     }
-    print(json.dumps(line))
+    args.emit(line)
 
 
 def run_pipeline(args):
@@ -434,7 +434,7 @@ def run_pipeline(args):
             "cpu_baseline": None, "clocks": clocks,
             "stage_blocks": ranges, "stage_compute_ms": [round(t.item(), 3) for t in per_stage], "stage_hop_bytes": rows * n_tok * MODEL_1P3B["dim"] * 2,
         }
-        print(json.dumps(line))
+        args.emit(line)
     dist.destroy_process_group()
 
 
@@ -452,6 +452,12 @@ def main():
         MODEL_1P3B.update(dim=5120, ffn_dim=13824, num_heads=40, num_layers=40)
         LEVELS[:] = [1000, 750, 500, 250]
     args.warmup = max(args.warmup, 0)
+    # Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line
+    # there, so everything but that line goes to stderr.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    args.emit = lambda line: os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if args.impl == "reference":
         return run_reference_arm(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
