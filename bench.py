@@ -9,7 +9,9 @@ bf16, 480x832 video (latent 16 x 60 x 104 per frame, 1560 tokens per latent fram
 1 sink + 20 ring latent frames.  The stream is first advanced until the ring is full and wrapping;
 every warm-up and timed step is then one chunk step (8 video frames) against the full cache.
 N > 1: the same model split into N contiguous block ranges, one rank per GPU, stage activations
-passed rank to rank over NCCL (one chunk in flight per stage).
+passed rank to rank over NCCL (one chunk in flight per stage).  The timed region is steady state:
+the warm-up leaves rank r exactly r chunks behind rank 0, then every rank runs K chunk steps between
+the two barriers, so K chunks enter the pipeline and K leave it inside the region.
 One JSON line is printed by rank 0.  `--impl reference` times the CPU restatement of the
 reference's attention path on the host cores instead.
 """
@@ -361,18 +363,22 @@ def run_pipeline(args):
             x = src(i) if rank == 0 else None
             return runner.step(i, x, cs, ce, None, last=last)
 
-        def phase(n, src, sink=None):
-            """n chunk steps, then empty the ring so that the barrier / device synchronise that
-            follows cannot wait on a transfer whose peer is itself waiting at the barrier."""
+        def phase(n, src, sink=None, keep_full=True):
+            """n chunk steps on this rank.  keep_full: the ring stays full across the barrier that
+            follows - every rank pauses with the packet for its next step already received and its
+            own send completed (`park`), so the device synchronise cannot wait on a peer and the
+            next phase starts in steady state.  Otherwise the ring is emptied (`quiesce`)."""
             for j in range(n):
                 out = one_step(src, last=(j == n - 1))
                 if sink is not None and out is not None:
                     sink(out)
-            runner.quiesce()
+            runner.park() if keep_full else runner.quiesce()
 
         resident = lambda i: dev_chunks[i % n_host]
-        phase(12 + world, resident)                       # fill the ring caches until they wrap
-        phase(max(args.warmup, 1), resident)
+        phase(12 + world, resident, keep_full=False)      # fill the K/V caches until they wrap
+        # warm-up, staggered: rank r stops r chunks behind rank 0, which is where a running stream
+        # has it; from here on every rank runs the same number of steps per phase
+        phase(max(args.warmup, 1) + (world - 1 - rank), resident)
         barrier()
         ops.read_status(device)
 
@@ -385,7 +391,7 @@ def run_pipeline(args):
         barrier()
         runner.stage_events = []
         e0.record()
-        phase(args.steps, resident)                       # ring starts empty and ends empty
+        phase(args.steps, resident)                       # K steps on every rank; K chunks enter, K leave
         e1.record()
         barrier()
         clocks = sampler.stop() if rank == 0 else None

@@ -118,6 +118,25 @@ class PipelineStageRunner:
                                                   pkt.ends, None, pkt.latents.clone()))
         self.link.drain()
 
+    def park(self) -> None:
+        """Pause with the ring still full, for a barrier or a device-wide synchronise between two
+        runs of steps.  Precondition: the ranks are staggered as in steady state, rank r having
+        processed exactly r chunks fewer than rank 0, so that one packet is travelling on every
+        edge.  Each rank takes that packet into its receive buffer (the next `step()` consumes it)
+        and waits for its own send; afterwards nothing is in flight and nothing was dropped.  A
+        rank whose upstream peer did not send raises on the host after the link's timeout instead
+        of leaving a receive waiting on the GPU."""
+        up = self.link.up
+        if self.role == "input":
+            due = self.items - (self.world - 1) - self.received - len(up.posted)
+        else:
+            due = 1 - len(up.posted)
+        if due > 1:
+            raise RuntimeError("park(): more than one packet outstanding; ranks are not staggered by one chunk")
+        if due == 1:
+            self.link.post_recv(confirm_sent=True)
+        self.link.drain()
+
     def finish(self) -> None:
         """End of stream: same as quiesce()."""
         self.quiesce()

@@ -135,13 +135,21 @@ class StageLink:
                 dist.barrier()
 
     # ------------------------------------------------------------------ receive side
-    def post_recv(self) -> None:
+    def post_recv(self, confirm_sent: bool = False) -> None:
         """Post the receive of the next packet from the previous stage.  Call it right after
         `recv()` returned and before enqueuing the compute that consumes that packet, so that the
-        transfer only waits for work that is already ahead of it."""
+        transfer only waits for work that is already ahead of it.
+
+        `confirm_sent=True` first waits on the host for the packet's metadata message, which the
+        sender issues together with the payload: if the peer never sent, that wait runs into the
+        group's timeout and raises, and no device-side receive is left waiting on the GPU."""
         e = self.up
         i = e.next
         e.next = (i + 1) % len(e.bufs)
+        if confirm_sent:
+            e.meta_works[i] = dist.irecv(e.meta[i], src=e.peer, group=e.meta_group)
+            e.meta_works[i].wait()
+            e.meta_works[i] = None
         if self._side is not None:
             # order after everything already enqueued on the compute stream (the previous user of
             # this buffer), but not after what the caller enqueues next
@@ -150,7 +158,8 @@ class StageLink:
                 e.works[i] = dist.irecv(e.bufs[i], src=e.peer, group=e.group)
         else:
             e.works[i] = dist.irecv(e.bufs[i], src=e.peer, group=e.group)
-        e.meta_works[i] = dist.irecv(e.meta[i], src=e.peer, group=e.meta_group)
+        if not confirm_sent:
+            e.meta_works[i] = dist.irecv(e.meta[i], src=e.peer, group=e.meta_group)
         e.posted.append(i)
 
     def recv(self) -> StagePacket:
@@ -160,8 +169,11 @@ class StageLink:
         if not e.posted:
             self.post_recv()
         i = e.posted.popleft()
-        e.meta_works[i].wait()
+        if e.meta_works[i] is not None:    # None: already taken in by post_recv(confirm_sent=True)
+            e.meta_works[i].wait()
+            e.meta_works[i] = None
         e.works[i].wait()          # NCCL: makes the current stream wait; gloo: blocks
+        e.works[i] = None
         m = e.meta[i].tolist()
         buf = e.bufs[i]
         act = buf[:self.act_numel].view(self.act_shape) if self._up_has_act else None

@@ -41,7 +41,7 @@ class _Patch:
         setattr(obj, name, value)
 
 
-def _worker_pipeline(rank, world, port, ranges, quiesce_every, q):
+def _worker_pipeline(rank, world, port, ranges, quiesce_every, q, park_at=()):
     try:
         _init(rank, world, port)
         import fake_ops
@@ -70,6 +70,9 @@ def _worker_pipeline(rank, world, port, ranges, quiesce_every, q):
                     outs.append(o.clone().numpy())
                 if last:
                     runner.quiesce()       # ring emptied mid-stream; results must not change
+                if i + rank in park_at:    # rank r is r chunks behind rank 0: the ring stays full
+                    runner.park()
+                    dist.barrier()
                 states.append(snapshot(pipe, runner.block_range[0] if rank == 0 else runner.block_range[1] - 1))
             runner.finish()
         q.put((rank, "ok", outs, states))
@@ -84,7 +87,10 @@ def _run(target, world, *args, timeout=240):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=target, args=(r, world, port, *args, q)) for r in range(world)]
+    extra = args[-1] if args and isinstance(args[-1], dict) else None
+    if extra is not None:
+        args = args[:-1]
+    procs = [ctx.Process(target=target, args=(r, world, port, *args, q), kwargs=extra or {}) for r in range(world)]
     for p in procs:
         p.start()
     results = {}
@@ -116,6 +122,35 @@ def test_two_rank_pipeline_matches_reference_fixture(quiesce_every):
         for key in ("global_end", "local_end", "evict_idx", "current_step"):
             assert res[0][2][i][key] == meta["steps"][i]["stageA_layer0"][key]
             assert res[1][2][i][key] == meta["steps"][i]["stageB_layerL"][key]
+
+
+def test_parking_a_full_ring_at_a_barrier_changes_nothing():
+    """Staggered ranks pause with one packet on every edge (park + barrier), twice, and go on:
+    same outputs and index state as the uninterrupted stream."""
+    case = cases.MODEL_CASES["m_stages"]
+    meta, z = cases.load_fixture("m_stages")
+    nblk, split = cases.MODEL_KW["num_layers"], case["split"]
+    res = _run(_worker_pipeline, 2, [[0, split], [split, nblk]], 0, {"park_at": (1, 3, 4)})
+    for r, v in res.items():
+        assert v[0] == "ok", v[1]
+    outs = res[1][1]
+    assert len(outs) == case["chunks"]
+    for i, o in enumerate(outs):
+        assert np.abs(o - z[f"out_{i}"]).max() < 5e-4, i
+    for i in range(case["chunks"]):
+        assert res[0][2][i]["global_end"] == meta["steps"][i]["stageA_layer0"]["global_end"]
+        assert res[1][2][i]["global_end"] == meta["steps"][i]["stageB_layerL"]["global_end"]
+
+
+def test_three_rank_ring_parks_and_resumes():
+    plain = _run(_worker_pipeline, 3, [[0, 1], [1, 2], [2, 3]], 0)
+    parked = _run(_worker_pipeline, 3, [[0, 1], [1, 2], [2, 3]], 0, {"park_at": (2, 4)})
+    for res in (plain, parked):
+        for r, v in res.items():
+            assert v[0] == "ok", v[1]
+    assert len(parked[2][1]) == len(plain[2][1])
+    for a, b in zip(parked[2][1], plain[2][1]):
+        assert np.array_equal(a, b)
 
 
 def test_three_rank_pipeline_runs_with_a_middle_stage():
