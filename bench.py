@@ -212,8 +212,63 @@ class ChunkSchedule:
         return cur
 
 
+def use_library_ops():
+    """Comparison arm (`--impl library`): the same model and stream, but the three cache kernels are
+    replaced by the calls the reference makes on a GPU - the fp64 complex rope chain with slice
+    writes into the cache (models/wan/causal_model.py:94-108, 321-322), flash_attn_with_kvcache
+    (:353-358), flash_attn_func for the text cross-attention (wan/modules/attention.py) - and the
+    block's norm / modulation / gate chains run as separate PyTorch ops.  The slot bookkeeping stays
+    ours (host integers, no device read-backs), so this arm is an upper bound on what the
+    reference's own loop would reach.  Library kernels only: `gpu_launches` is reported as 0."""
+    import math
+    from flash_attn import flash_attn_func, flash_attn_with_kvcache
+    from streamdiffusionv2_b200 import ops, wan_model
+
+    def rope_kv_append(q, k, v, k_cache, v_cache, table, grid, start_frames, dst_begin, *, q_out=None,
+                       index_tensors=None, index_values=None):
+        B, n, H, D = q.shape
+        f, h, w = (int(x) for x in grid)
+        tc = torch.view_as_complex(table)
+        c = D // 2
+        ct, ch = c - 2 * (c // 3), c // 3
+        if q_out is None:
+            q_out = torch.empty((B, n, H, D), dtype=q.dtype, device=q.device)
+        with ops._Logged("rope_kv_append", 6.0 * B * n * H * D * q.element_size()):
+            for b in range(B):
+                sf = int(start_frames[b])
+                mult = torch.cat([tc[sf:sf + f, :ct].view(f, 1, 1, -1).expand(f, h, w, -1),
+                                  tc[:h, ct:ct + ch].view(1, h, 1, -1).expand(f, h, w, -1),
+                                  tc[:w, ct + ch:].view(1, 1, w, -1).expand(f, h, w, -1)], dim=-1).reshape(n, 1, -1)
+                rq = torch.view_as_complex(q[b].to(torch.float64).reshape(n, H, -1, 2)) * mult
+                rk = torch.view_as_complex(k[b].to(torch.float64).reshape(n, H, -1, 2)) * mult
+                q_out[b] = torch.view_as_real(rq).flatten(2).type_as(q)
+                d = int(dst_begin[b])
+                k_cache[b:b + 1, d:d + n] = torch.view_as_real(rk).flatten(2).type_as(k).unsqueeze(0)
+                v_cache[b:b + 1, d:d + n] = v[b:b + 1]
+                if index_tensors is not None:
+                    index_tensors[0][b:b + 1].fill_(int(index_values[0][b]))
+                    index_tensors[1][b:b + 1].fill_(int(index_values[1][b]))
+        return q_out
+
+    def attn_kvcache(q, k_cache, v_cache, seq_lens, *, out=None, softmax_scale=None):
+        B, n, H, D = q.shape
+        lens = torch.tensor([int(x) for x in seq_lens[:B]], dtype=torch.int32, device=q.device)
+        with ops._Logged("attn_kvcache", 4.0 * n * D * H * float(sum(int(x) for x in seq_lens[:B]))):
+            return flash_attn_with_kvcache(q, k_cache, v_cache, cache_seqlens=lens, softmax_scale=softmax_scale)
+
+    def cross_attn(q, k, v, *, out=None, softmax_scale=None):
+        B = q.shape[0]
+        with ops._Logged("cross_attn", 4.0 * B * q.shape[1] * q.shape[3] * q.shape[2] * k.shape[1]):
+            return flash_attn_func(q, k.expand(B, -1, -1, -1), v.expand(B, -1, -1, -1), softmax_scale=softmax_scale)
+
+    ops.rope_kv_append, ops.attn_kvcache, ops.cross_attn = rope_kv_append, attn_kvcache, cross_attn
+    wan_model._fusable = lambda x: False
+
+
 def run_single_gpu(args):
     from streamdiffusionv2_b200 import ops
+    if args.impl == "library":
+        use_library_ops()
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     peaks = measured_peaks()
@@ -311,6 +366,10 @@ def run_single_gpu(args):
                             "avg_launch_ms": app_ms, "bytes_per_launch": app_bytes, "traffic": None},
         "cpu_baseline": cpu, "clocks": clocks,
     }
+    if args.impl == "library":
+        line.update(impl="library", gpu_launches=0, gpu_launches_by_kernel={})
+        line["roofline"]["kernel"] = "flash_attn_with_kvcache (library)"
+        line["roofline_append"]["kernel"] = "fp64 complex rope chain + slice writes (PyTorch ops)"
     args.emit(line)
 
 
@@ -449,7 +508,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=24)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"],
+                    help="reference: the CPU restatement on the host cores; library: comparison arm, N=1 only, "
+                         "the reference's GPU op chain (flash-attn, PyTorch ops) under the same model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--model", default="1.3b", choices=["1.3b", "14b"],
                     help="1.3b is the headline workload; 14b = 40 blocks, dim 5120, 40 heads, 4 denoise levels")
@@ -468,6 +529,8 @@ def main():
         return run_reference_arm(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return run_single_gpu(args)
+    if args.impl == "library":
+        raise SystemExit("--impl library is a single-GPU comparison")
     return run_pipeline(args)
 
 
