@@ -286,6 +286,8 @@ def run_single_gpu(args):
     with torch.no_grad():
         pipe.prepare(text_prompts=["synthetic"], device=device, dtype=torch.bfloat16, noise=first, current_start=0,
                      current_end=FRAME_TOKENS * (1 + FRAMES_PER_CHUNK))
+        if args.graphs and args.impl == "ours":
+            pipe.enable_step_graphs()      # steady-state steps replay the DiT forward from a CUDA graph
         fill = 0
         while min(pipe.kv_cache1[0]["_sdv2_host"].local_end) < CACHE_FRAMES * FRAME_TOKENS or fill < 11:
             cs, ce = sched.next()
@@ -298,7 +300,7 @@ def run_single_gpu(args):
         ops.read_status(device)
 
         # ---- timed region 1: inputs resident in HBM
-        log = ops.LaunchLog(timed=True)
+        log = ops.LaunchLog(timed=not args.graphs)
         ops.set_launch_log(log)
         sampler = ClockSampler(0)
         sampler.start()
@@ -329,9 +331,23 @@ def run_single_gpu(args):
         ms_e2e = e2.elapsed_time(e3)
         ops.read_status(device)
 
+        # ---- per-kernel durations: launches inside a graph cannot be bracketed by events, so the
+        # same steps are run once more from Python with every launch of ours timed
+        tlog = log
+        if args.graphs:
+            graphs, pipe.step_graphs = pipe.step_graphs, None
+            tlog = ops.LaunchLog(timed=True)
+            ops.set_launch_log(tlog)
+            for i in range(min(args.steps, 6)):
+                cs, ce = sched.next()
+                pipe.inference_stream(dev_chunks[i % n_host], cs, ce)
+            torch.cuda.synchronize()
+            ops.set_launch_log(None)
+            pipe.step_graphs = graphs
+
     launches = sum(log.counts.values())
-    att = log.durations_ms("attn_kvcache")
-    app = log.durations_ms("rope_kv_append")
+    att = tlog.durations_ms("attn_kvcache")
+    app = tlog.durations_ms("rope_kv_append")
     att_ms = statistics.mean(att)
     att_flops = log.work["attn_kvcache"] / log.counts["attn_kvcache"]
     app_ms = statistics.mean(app)
@@ -359,12 +375,16 @@ def run_single_gpu(args):
         "roofline": {"kernel": "attn_kvcache (tcgen05)", "bound": "tensor", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
                      "traffic": None, "avg_launch_ms": att_ms, "flops_per_launch": att_flops,
-                     "share_of_step": att_ms * log.counts["attn_kvcache"] / ms},
+                     "share_of_step": att_ms * log.counts["attn_kvcache"] / ms,
+                     "timed_in": "launch-by-launch pass of the same steps after the timed region (graph replay "
+                                 "hides single launches from events)" if args.graphs else "the timed region"},
         "roofline_append": {"kernel": "rope_kv_append", "bound": "hbm", "achieved": app_bytes / (app_ms * 1e-3) / 1e9,
                             "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": app_bytes / (app_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                             "avg_launch_ms": app_ms, "bytes_per_launch": app_bytes, "traffic": None},
         "cpu_baseline": cpu, "clocks": clocks,
+        "step_graphs": None if pipe.step_graphs is None else {"replayed_steps": pipe.step_graphs.replays,
+                                                              "eager_steps": pipe.step_graphs.eager_steps},
     }
     if args.impl == "library":
         line.update(impl="library", gpu_launches=0, gpu_launches_by_kernel={})
@@ -413,6 +433,8 @@ def run_pipeline(args):
         link = StageLink(rank, world, device, (rows, n_tok, MODEL_1P3B["dim"]),
                          (rows, FRAMES_PER_CHUNK, 16, h, w), dtype=torch.bfloat16, timeout_s=90)
         runner = PipelineStageRunner(pipe, link, rank, world, ranges, prefetch=bool(int(os.environ.get("SDV2_PREFETCH", "0"))))
+        if args.graphs:
+            pipe.enable_step_graphs()      # recorded at this rank's first steady step after the ring was emptied
         chunk = [0]
 
         def one_step(src, last=False):
@@ -441,7 +463,7 @@ def run_pipeline(args):
         barrier()
         ops.read_status(device)
 
-        log = ops.LaunchLog(timed=True)
+        log = ops.LaunchLog(timed=not args.graphs)
         ops.set_launch_log(log)
         sampler = ClockSampler(local)
         if rank == 0:
@@ -469,7 +491,17 @@ def run_pipeline(args):
         ms_e2e = e2.elapsed_time(e3)
         ops.read_status(device)
 
-    att = log.durations_ms("attn_kvcache")
+        tlog = log
+        if args.graphs:                    # per-kernel durations: a launch-by-launch pass of the same steps
+            graphs, pipe.step_graphs = pipe.step_graphs, None
+            tlog = ops.LaunchLog(timed=True)
+            ops.set_launch_log(tlog)
+            phase(4, resident)
+            barrier()
+            ops.set_launch_log(None)
+            pipe.step_graphs = graphs
+
+    att = tlog.durations_ms("attn_kvcache")
     stats = torch.tensor([ms, ms_e2e, float(sum(log.counts.values())), statistics.mean(att) if att else 0.0],
                          dtype=torch.float64, device=device)
     mx = stats.clone()
@@ -481,7 +513,7 @@ def run_pipeline(args):
     if rank == 0:
         ms_max, ms_e2e_max = mx[0].item(), mx[1].item()
         att_ms = sm[3].item() / world
-        att_flops = log.work["attn_kvcache"] / log.counts["attn_kvcache"]
+        att_flops = tlog.work["attn_kvcache"] / tlog.counts["attn_kvcache"]
         achieved = att_flops / (att_ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
         line = {
@@ -512,6 +544,8 @@ def main():
                     help="reference: the CPU restatement on the host cores; library: comparison arm, N=1 only, "
                          "the reference's GPU op chain (flash-attn, PyTorch ops) under the same model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graphs", dest="graphs", action="store_false",
+                    help="launch every op of every step from Python instead of replaying steady steps from a CUDA graph")
     ap.add_argument("--model", default="1.3b", choices=["1.3b", "14b"],
                     help="1.3b is the headline workload; 14b = 40 blocks, dim 5120, 40 heads, 4 denoise levels")
     args = ap.parse_args()

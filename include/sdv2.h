@@ -94,6 +94,28 @@ int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view*
                         int dtype, int* status_dev, void* stream);
 
 /*
+ * Same operation with the per-row slot parameters in device memory, for launches that must not
+ * carry per-step values - a launch recorded in a CUDA graph is replayed with the values the host
+ * wrote into the array since.  No reference counterpart (the reference passes Python ints).
+ *
+ * step_params_dev: device int64 [4][rows], 8-byte aligned: start_frame | dst_begin |
+ *   global_end value | local_end value, read by the kernel when it runs.  The host cannot check
+ *   them, so the kernel does: if a slot would leave the cache or a frame the rope table, the
+ *   launch writes nothing and records that in *status_dev, and sdv2_read_status then returns
+ *   SDV2_ERR_INVALID_ARG.  The caller orders its update of the array before the launch (same
+ *   stream) and must not overwrite it while a launch that reads it is still pending.
+ * Everything else as for sdv2_rope_kv_append.
+ */
+int sdv2_rope_kv_append_indirect(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v,
+                                 const sdv2_view* q_out, const sdv2_view* k_cache, const sdv2_view* v_cache,
+                                 int rows, int new_tokens, int heads, int head_dim, int64_t cache_tokens,
+                                 const double* rope_table_dev, int table_rows,
+                                 int grid_f, int grid_h, int grid_w,
+                                 const int64_t* step_params_dev,
+                                 int64_t* global_end_dev, int64_t* local_end_dev,
+                                 int dtype, int* status_dev, void* stream);
+
+/*
  * Attention of the new queries over the wrapped cache: out[b] = softmax(q[b] k[b,:L_b]^T * scale)
  * v[b,:L_b] with L_b = seq_lens[b], no causal or window mask (the window is the cache content).
  *
@@ -184,7 +206,8 @@ int sdv2_gate_residual(const void* x, const void* y, const void* gate, int64_t m
                        int frames, int tokens_per_frame, int dim, void* stream);
 
 /* Synchronises `stream`, reads the status word at the start of a workspace and clears it.
- * Returns SDV2_OK, SDV2_ERR_TIMEOUT (a device-side wait ran out; *detail = where) or
+ * Returns SDV2_OK, SDV2_ERR_TIMEOUT (a device-side wait ran out; *detail = where),
+ * SDV2_ERR_INVALID_ARG (device-resident slot parameters were out of range; nothing was written) or
  * SDV2_ERR_CUDA. */
 int sdv2_read_status(void* workspace_dev, int* detail, void* stream);
 

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libsdv2.so")
 MAX_ROWS = 64
 DTYPE_BF16, DTYPE_F32 = 0, 1
 ERR_TIMEOUT = -5
+ERR_INVALID_ARG = -1
 
 
 class View(C.Structure):
@@ -39,6 +40,10 @@ _SIGNATURES = {
                                                                C.c_void_p, C.c_void_p,
                                                                C.POINTER(C.c_int64), C.POINTER(C.c_int64),
                                                                C.c_int, C.c_void_p, C.c_void_p]),
+    "sdv2_rope_kv_append_indirect": (C.c_int, [C.POINTER(View)] * 6 + [C.c_int, C.c_int, C.c_int, C.c_int,
+                                                                        C.c_int64, C.c_void_p, C.c_int, C.c_int,
+                                                                        C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                                                        C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "sdv2_attn_kvcache": (C.c_int, [C.POINTER(View)] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64,
                                                              C.POINTER(C.c_int32), C.c_float, C.c_void_p,
                                                              C.c_size_t, C.c_void_p]),

@@ -24,6 +24,15 @@ from . import ops
 from .ring_state import RingState
 
 _start_cache = {}
+_step_recorder = None
+
+
+def set_step_recorder(recorder) -> None:
+    """While set (a step is being recorded into a CUDA graph, see step_graph.py), the append kernel
+    of every layer reads its per-row slot parameters from the recorder's device array instead of
+    receiving them as launch arguments."""
+    global _step_recorder
+    _step_recorder = recorder
 
 
 def host_starts(current_start, rows: int) -> List[int]:
@@ -99,11 +108,17 @@ def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_
     sink_tokens = attn_module.sink_size * frame_tokens
     adaptive = sink_tokens > 0 and attn_module.adapt_sink_thr > -1 and n_new <= frame_tokens
 
+    if _step_recorder is not None and adaptive:
+        raise RuntimeError("the adaptive sink test reads the device back and cannot be recorded in a graph")
     if not adaptive:
         dst, seq_lens = state.plan(kv_cache, attn_module, starts, n_new, frame_tokens)
+        extra = {}
+        if _step_recorder is not None:
+            extra["step_params"] = _step_recorder.layer_params(attn_module, kv_cache, start_frames, dst, state,
+                                                               seq_lens, n_new, frame_tokens)
         roped_q = ops.rope_kv_append(q, k, v, kv_cache["k"], kv_cache["v"], table, (f, gh, gw), start_frames,
                                      dst, index_tensors=index_tensors,
-                                     index_values=(state.global_end, state.local_end))
+                                     index_values=(state.global_end, state.local_end), **extra)
     else:
         # the slot of row i depends on roped k and on the cache as rows < i left it: rope into a
         # staging chunk first, then test and place row by row

@@ -155,13 +155,15 @@ const char* sdv2_strerror(int code) {
 
 int sdv2_last_cuda_error(void) { return g_last_cuda_error; }
 
-int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, const sdv2_view* q_out,
-                        const sdv2_view* k_cache, const sdv2_view* v_cache, int rows, int new_tokens, int heads,
-                        int head_dim, int64_t cache_tokens, const double* rope_table_dev, int table_rows,
-                        int grid_f, int grid_h, int grid_w, const int64_t* start_frame,
-                        const int64_t* dst_begin, int64_t* global_end_dev, int64_t* local_end_dev,
-                        const int64_t* global_end_val, const int64_t* local_end_val, int dtype, int* status_dev,
-                        void* stream) {
+// Shared by the two append entry points: slot parameters either in the four host arrays or in
+// `step_params_dev` (device, [4][rows]).
+static int append_common(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, const sdv2_view* q_out,
+                         const sdv2_view* k_cache, const sdv2_view* v_cache, int rows, int new_tokens, int heads,
+                         int head_dim, int64_t cache_tokens, const double* rope_table_dev, int table_rows,
+                         int grid_f, int grid_h, int grid_w, const int64_t* start_frame,
+                         const int64_t* dst_begin, int64_t* global_end_dev, int64_t* local_end_dev,
+                         const int64_t* global_end_val, const int64_t* local_end_val,
+                         const int64_t* step_params_dev, int dtype, int* status_dev, void* stream) {
   if (rows <= 0 || new_tokens <= 0 || heads <= 0 || cache_tokens <= 0 || table_rows <= 0) return SDV2_ERR_INVALID_ARG;
   if (grid_f <= 0 || grid_h <= 0 || grid_w <= 0) return SDV2_ERR_INVALID_ARG;
   if (static_cast<int64_t>(grid_f) * grid_h * grid_w != new_tokens) return SDV2_ERR_INVALID_ARG;
@@ -169,10 +171,14 @@ int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view*
   if (rows > SDV2_MAX_ROWS) return SDV2_ERR_UNSUPPORTED_SHAPE;
   const int esize = dtype == SDV2_DTYPE_BF16 ? 2 : 4;
   if (head_dim <= 0 || head_dim % (16 / esize) || head_dim % 2) return SDV2_ERR_UNSUPPORTED_SHAPE;
-  if (rope_table_dev == nullptr || start_frame == nullptr || dst_begin == nullptr) return SDV2_ERR_INVALID_ARG;
+  const bool indirect = step_params_dev != nullptr;
+  if (rope_table_dev == nullptr) return SDV2_ERR_INVALID_ARG;
+  if (!indirect && (start_frame == nullptr || dst_begin == nullptr)) return SDV2_ERR_INVALID_ARG;
+  if (indirect && (reinterpret_cast<uintptr_t>(step_params_dev) & 7u)) return SDV2_ERR_MISALIGNED;
   if (!aligned16(rope_table_dev)) return SDV2_ERR_MISALIGNED;
   if ((global_end_dev == nullptr) != (local_end_dev == nullptr)) return SDV2_ERR_INVALID_ARG;
-  if (global_end_dev != nullptr && (global_end_val == nullptr || local_end_val == nullptr)) return SDV2_ERR_INVALID_ARG;
+  if (!indirect && global_end_dev != nullptr && (global_end_val == nullptr || local_end_val == nullptr))
+    return SDV2_ERR_INVALID_ARG;
   int rc;
   const sdv2_view* views[6] = {q, k, v, q_out, k_cache, v_cache};
   for (const sdv2_view* vw : views)
@@ -181,7 +187,7 @@ int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view*
 
   sdv2::AppendParams p;
   memset(&p, 0, sizeof(p));
-  for (int b = 0; b < rows; ++b) {
+  for (int b = 0; b < rows && !indirect; ++b) {
     // the reference fails with a shape mismatch where these hold; fail loudly instead of writing
     // outside the cache or reading past the rope table
     if (dst_begin[b] < 0 || dst_begin[b] + new_tokens > cache_tokens) return SDV2_ERR_INVALID_ARG;
@@ -206,9 +212,37 @@ int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view*
   p.cols_h = p.half / 3;
   p.global_end_dev = global_end_dev;
   p.local_end_dev = local_end_dev;
+  p.step_dev = step_params_dev;
+  p.cache_tokens = cache_tokens;
+  p.table_rows = table_rows;
+  p.grid_f = grid_f;
   p.status = status_dev;
   cudaError_t e = sdv2::launch_rope_kv_append(p, dtype, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? SDV2_OK : cuda_fail(e);
+}
+
+int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, const sdv2_view* q_out,
+                        const sdv2_view* k_cache, const sdv2_view* v_cache, int rows, int new_tokens, int heads,
+                        int head_dim, int64_t cache_tokens, const double* rope_table_dev, int table_rows,
+                        int grid_f, int grid_h, int grid_w, const int64_t* start_frame,
+                        const int64_t* dst_begin, int64_t* global_end_dev, int64_t* local_end_dev,
+                        const int64_t* global_end_val, const int64_t* local_end_val, int dtype, int* status_dev,
+                        void* stream) {
+  return append_common(q, k, v, q_out, k_cache, v_cache, rows, new_tokens, heads, head_dim, cache_tokens,
+                       rope_table_dev, table_rows, grid_f, grid_h, grid_w, start_frame, dst_begin, global_end_dev,
+                       local_end_dev, global_end_val, local_end_val, nullptr, dtype, status_dev, stream);
+}
+
+int sdv2_rope_kv_append_indirect(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v,
+                                 const sdv2_view* q_out, const sdv2_view* k_cache, const sdv2_view* v_cache,
+                                 int rows, int new_tokens, int heads, int head_dim, int64_t cache_tokens,
+                                 const double* rope_table_dev, int table_rows, int grid_f, int grid_h, int grid_w,
+                                 const int64_t* step_params_dev, int64_t* global_end_dev, int64_t* local_end_dev,
+                                 int dtype, int* status_dev, void* stream) {
+  if (step_params_dev == nullptr) return SDV2_ERR_INVALID_ARG;
+  return append_common(q, k, v, q_out, k_cache, v_cache, rows, new_tokens, heads, head_dim, cache_tokens,
+                       rope_table_dev, table_rows, grid_f, grid_h, grid_w, nullptr, nullptr, global_end_dev,
+                       local_end_dev, nullptr, nullptr, step_params_dev, dtype, status_dev, stream);
 }
 
 size_t sdv2_attn_workspace_bytes(int rows, int q_tokens, int heads, int head_dim) {
@@ -271,7 +305,7 @@ int sdv2_read_status(void* workspace_dev, int* detail, void* stream) {
   e = cudaMemsetAsync(workspace_dev, 0, sizeof(int), s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) return cuda_fail(e);
-  return SDV2_ERR_TIMEOUT;
+  return (word & 0xFF) == 10 ? SDV2_ERR_INVALID_ARG : SDV2_ERR_TIMEOUT;  // 10: BAD_STEP_PARAMS
 }
 
 int sdv2_selftest_umma(const void* a_dev, const void* b_dev, const void* p_dev, const void* v_dev,

@@ -38,7 +38,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Where a bounded wait gave up (stored in the status word's low bits).
 enum WaitSite : int {
   WAIT_Q_FULL = 1, WAIT_KV_FULL = 2, WAIT_KV_EMPTY = 3, WAIT_S_FULL = 4, WAIT_P_FULL = 5,
-  WAIT_O_FULL = 6, WAIT_PROBE = 7, WAIT_DRAIN = 8, WAIT_TILE_FREE = 9
+  WAIT_O_FULL = 6, WAIT_PROBE = 7, WAIT_DRAIN = 8, WAIT_TILE_FREE = 9,
+  BAD_STEP_PARAMS = 10  // not a wait: device-resident slot parameters were out of range, nothing written
 };
 
 // Spin on an mbarrier phase with a cycle budget.  `abort_flag` lives in shared memory and is

@@ -75,13 +75,39 @@ __device__ __forceinline__ double2 table_entry(const AppendParams& p, int col, i
   return __ldg(p.table + row * p.half + col);
 }
 
+// Per-row slot parameters come from the launch parameters or, for launches that must not carry
+// per-step values (a captured graph), from a device array the host refreshes between steps.
+__device__ __forceinline__ int64_t row_start_frame(const AppendParams& p, int b) {
+  return p.step_dev != nullptr ? p.step_dev[b] : p.start_frame[b];
+}
+__device__ __forceinline__ int64_t row_dst_begin(const AppendParams& p, int b) {
+  return p.step_dev != nullptr ? p.step_dev[p.rows + b] : p.dst_begin[b];
+}
+
+// Device-resident parameters cannot be validated by the host: every thread checks them (the same
+// few cached loads) and the whole launch writes nothing when a slot would leave the cache or a
+// frame the rope table.  Block 0 records that in the status word.
+__device__ __forceinline__ bool step_params_ok(const AppendParams& p) {
+  if (p.step_dev == nullptr) return true;
+  bool ok = true;
+  for (int b = 0; b < p.rows; ++b) {
+    const int64_t f = p.step_dev[b], d = p.step_dev[p.rows + b];
+    ok = ok && f >= 0 && f + p.grid_f <= p.table_rows && d >= 0 && d + p.tokens <= p.cache_tokens;
+  }
+  return ok;
+}
+
 __device__ __forceinline__ void write_index(const AppendParams& p) {
   if (p.global_end_dev != nullptr) {
     for (int b = 0; b < p.rows; ++b) {
-      p.global_end_dev[b] = p.global_end_val[b];
-      p.local_end_dev[b] = p.local_end_val[b];
+      p.global_end_dev[b] = p.step_dev != nullptr ? p.step_dev[2 * p.rows + b] : p.global_end_val[b];
+      p.local_end_dev[b] = p.step_dev != nullptr ? p.step_dev[3 * p.rows + b] : p.local_end_val[b];
     }
   }
+}
+
+__device__ __forceinline__ void report_bad_step_params(const AppendParams& p) {
+  if (p.status != nullptr) atomicCAS(p.status, 0, static_cast<int>(BAD_STEP_PARAMS));
 }
 
 // ------------------------------------------------------------------------------------------
@@ -93,7 +119,12 @@ __global__ void __launch_bounds__(256) rope_kv_append_direct_kernel(const __grid
   constexpr int kElems = 2 * kPairs;
   const int vph = p.head_dim / kElems;
   const int tok_per_block = 256 / vph;
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) write_index(p);
+  const bool first = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+  if (!step_params_ok(p)) {
+    if (first) report_bad_step_params(p);
+    return;
+  }
+  if (first) write_index(p);
   const int tl = fast_div(threadIdx.x, p.magic_vph);
   const int c = threadIdx.x - tl * vph;
   const int t = blockIdx.x * tok_per_block + tl;
@@ -106,8 +137,8 @@ __global__ void __launch_bounds__(256) rope_kv_append_direct_kernel(const __grid
   const int x = rem - y * p.grid_w;
   double2 cs[kPairs];
 #pragma unroll
-  for (int i = 0; i < kPairs; ++i) cs[i] = table_entry(p, c * kPairs + i, p.start_frame[b] + f, y, x);
-  const int64_t slot = p.dst_begin[b] + t;
+  for (int i = 0; i < kPairs; ++i) cs[i] = table_entry(p, c * kPairs + i, row_start_frame(p, b) + f, y, x);
+  const int64_t slot = row_dst_begin(p, b) + t;
   const int e0 = c * kElems;
   const T* qp = static_cast<const T*>(p.q.ptr) + b * p.q.stride_row + t * p.q.stride_tok + h * p.q.stride_head + e0;
   const T* kp = static_cast<const T*>(p.k.ptr) + b * p.k.stride_row + t * p.k.stride_tok + h * p.k.stride_head + e0;
@@ -172,6 +203,10 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (!step_params_ok(p)) {  // uniform over the grid: no barrier was touched, no copy issued
+    if (blockIdx.x == 0 && threadIdx.x == 0) report_bad_step_params(p);
+    return;
+  }
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -213,7 +248,7 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
         bulk_load(sbase + which * tensor_stride + j * row_bytes, src, row_bytes, bar0 + 8 * s);
       }
       double2* mult = reinterpret_cast<double2*>(gbase + s * stage_bytes + mult_off);
-      const int64_t frame0 = p.start_frame[b];
+      const int64_t frame0 = row_start_frame(p, b);
       const int n_ent = n * p.half;
       for (int e0 = plane_id; e0 < n_ent; e0 += kProducerWarps * 32 * kMultBatch) {
         double2 val[kMultBatch];  // all loads of a batch in flight before the first store
@@ -266,7 +301,7 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
       if (!ok) break;
       const uint8_t* sq = gbase + s * stage_bytes;
       const int n_vec = n * row_vecs;
-      const int64_t slot0 = p.dst_begin[b] + t0;
+      const int64_t slot0 = row_dst_begin(p, b) + t0;
       T* qo_base = static_cast<T*>(p.q_out.ptr) + b * p.q_out.stride_row + t0 * p.q_out.stride_tok;
       T* kc_base = static_cast<T*>(p.k_cache.ptr) + b * p.k_cache.stride_row + slot0 * p.k_cache.stride_tok;
       T* vc_base = static_cast<T*>(p.v_cache.ptr) + b * p.v_cache.stride_row + slot0 * p.v_cache.stride_tok;

@@ -23,6 +23,11 @@ struct AppendParams {
   int* status;              // optional device word that records an abandoned wait
   int64_t* global_end_dev;
   int64_t* local_end_dev;
+  // per-row slot parameters: either the four host-filled arrays below, or, when step_dev is set,
+  // a device array [4][rows] (start_frame | dst_begin | global_end | local_end) read by the kernel
+  const int64_t* step_dev;
+  int64_t cache_tokens;     // bounds for the device-resident parameters
+  int table_rows, grid_f;
   int64_t start_frame[SDV2_MAX_ROWS];
   int64_t dst_begin[SDV2_MAX_ROWS];
   int64_t global_end_val[SDV2_MAX_ROWS];

@@ -40,6 +40,10 @@ def set_launch_log(log: Optional[LaunchLog]) -> None:
     _log = log
 
 
+def current_launch_log() -> Optional[LaunchLog]:
+    return _log
+
+
 class _Logged:
     __slots__ = ("name", "work", "ev")
 
@@ -96,10 +100,15 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
                    start_frames: Sequence[int], dst_begin: Sequence[int], *,
                    q_out: Optional[torch.Tensor] = None,
                    index_tensors: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                   index_values: Optional[Tuple[Sequence[int], Sequence[int]]] = None) -> torch.Tensor:
+                   index_values: Optional[Tuple[Sequence[int], Sequence[int]]] = None,
+                   step_params: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rope q and k, write k/v of every row into cache slot [dst_begin[b], dst_begin[b]+N).
     q, k, v: [B, N, H, D]; caches [B, Smax, H, D]; table: float64 [rows, D/2, 2] on the device.
     Optionally stores index_values into the (global_end, local_end) int64 device tensors.
+    With `step_params` (device int64 [4, B], contiguous: start frames | slots | global ends |
+    local ends) the kernel reads those values from that tensor when it runs and the host-side
+    start_frames / dst_begin / index_values arguments are ignored: the launch then carries nothing
+    that changes from step to step and can be replayed from a CUDA graph.
     Returns the roped q ([B, N, H, D], contiguous)."""
     B, n_new, H, D = q.shape
     if q_out is None:
@@ -114,8 +123,20 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
         if not (g.is_contiguous() and l.is_contiguous()):
             raise ValueError("index tensors must be contiguous")
         ge_dev, le_dev = g.data_ptr(), l.data_ptr()
-        ge_val, le_val = N.i64_array(index_values[0]), N.i64_array(index_values[1])
+        if step_params is None:
+            ge_val, le_val = N.i64_array(index_values[0]), N.i64_array(index_values[1])
     views = [N.view(t) for t in (q, k, v, q_out, k_cache, v_cache)]
+    if step_params is not None:
+        if (step_params.dtype != torch.int64 or not step_params.is_contiguous() or step_params.numel() != 4 * B
+                or step_params.device != q.device):
+            raise ValueError("step_params must be a contiguous int64 [4, rows] tensor on the same device")
+        with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
+            rc = N.lib().sdv2_rope_kv_append_indirect(
+                *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
+                f, h, w, step_params.data_ptr(), ge_dev, le_dev, N.dtype_code(q.dtype),
+                workspace(q.device).data_ptr(), N.stream_ptr(q.device))
+        N.check(rc, "sdv2_rope_kv_append_indirect")
+        return q_out
     with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
         rc = N.lib().sdv2_rope_kv_append(
             *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
@@ -240,6 +261,9 @@ def read_status(device: torch.device) -> None:
     if rc == N.ERR_TIMEOUT:
         raise N.NativeError(rc, "attention kernel", f"device-side wait timed out at site {detail.value & 0xFF} "
                                                     f"(block {detail.value >> 8})")
+    if rc == N.ERR_INVALID_ARG and detail.value:
+        raise N.NativeError(rc, "rope_kv_append", "device-resident slot parameters were out of range; "
+                                                  "that launch wrote nothing")
     N.check(rc, "sdv2_read_status")
 
 

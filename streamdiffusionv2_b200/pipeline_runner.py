@@ -39,6 +39,7 @@ class PipelineStageRunner:
         self.received = 0         # stage 0: packets taken from the closing edge
         self._returned = deque()  # stage 0: packets taken in by quiesce(), not yet adopted
         self.stage_events = None  # set to [] to record (start, end) CUDA events around each stage compute
+        self._quiet = True        # nothing in flight on the links: a step may synchronise the device (graph recording)
 
     @property
     def owned_blocks(self) -> range:
@@ -71,7 +72,9 @@ class PipelineStageRunner:
                 link.post_recv()
             ev = self._mark()
             act, _ = pipe.inference(noise=noise, current_start=current_start, current_end=current_end,
-                                    current_step=current_step, block_mode="input", block_num=self.block_range)
+                                    current_step=current_step, block_mode="input", block_num=self.block_range,
+                                    allow_record=self._quiet)
+            self._quiet = False
             self._mark(ev)
             link.send(chunk_idx, act, pipe.hidden_states, pipe.generator.model.last_patched_x_shape,
                       pipe._starts_host, pipe._ends_host, -1 if current_step is None else int(current_step))
@@ -86,7 +89,8 @@ class PipelineStageRunner:
         out, pshape = pipe.inference(noise=pkt.latents, current_start=pkt.starts, current_end=pkt.ends,
                                      current_step=step, block_mode=self.role, block_num=self.block_range,
                                      patched_x_shape=pkt.patched_x_shape, block_x=pkt.activations,
-                                     starts_host=pkt.starts)
+                                     starts_host=pkt.starts, allow_record=self._quiet)
+        self._quiet = False
         self._mark(ev)
         if self.role == "middle":
             link.send(pkt.chunk_idx, out, pkt.latents, pkt.patched_x_shape, pkt.starts, pkt.ends, pkt.current_step)
@@ -117,6 +121,7 @@ class PipelineStageRunner:
                 self._returned.append(StagePacket(pkt.chunk_idx, pkt.current_step, pkt.patched_x_shape, pkt.starts,
                                                   pkt.ends, None, pkt.latents.clone()))
         self.link.drain()
+        self._quiet = True
 
     def park(self) -> None:
         """Pause with the ring still full, for a barrier or a device-wide synchronise between two
@@ -136,6 +141,7 @@ class PipelineStageRunner:
         if due == 1:
             self.link.post_recv(confirm_sent=True)
         self.link.drain()
+        self._quiet = True
 
     def finish(self) -> None:
         """End of stream: same as quiesce()."""

@@ -1,0 +1,174 @@
+"""Replay of a steady-state chunk step from a CUDA graph.
+
+Once every cache row has wrapped, a chunk step launches the same kernels with the same shapes and
+the same attention lengths every time; the only values that change are each row's rope start frame,
+its ring slot and the two index values the append kernel stores.  Those are read by the kernel from
+a small device array (`ops.rope_kv_append(step_params=...)`), so the whole DiT forward of a step
+(~500 launches for 30 blocks) is recorded once and replayed with a single launch, after one
+host->device copy of that array.  The host slot state is still advanced layer by layer with the
+same `RingState.plan` calls the eager path makes, so cache dicts, evict queues and host mirrors
+end up exactly as without graphs, and any step that does not match the recorded one (a row that
+has not wrapped yet, another shape, the adaptive sink test) simply runs eagerly.
+
+The reference has no counterpart: it launches every op from Python each step and reads device
+indices back in between (models/wan/causal_model.py:279-342).
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import causal_attention as CA
+from . import ops
+from .ring_state import RingState
+
+_PINNED_SLOTS = 4
+
+
+class _Recorder:
+    """Active while a forward is being captured: hands every layer its slice of the parameter
+    array and notes which (attention module, cache dict) pairs ran, in order."""
+
+    def __init__(self, params_dev: torch.Tensor, host: torch.Tensor):
+        self.params_dev, self.host = params_dev, host
+        self.layers: List[Tuple[object, dict]] = []
+        self.seq_lens: Optional[List[int]] = None
+        self.n_new = self.frame_tokens = 0
+
+    def layer_params(self, attn_module, kv_cache, start_frames, dst, state: RingState, seq_lens, n_new, frame_tokens):
+        i = len(self.layers)
+        if i >= self.params_dev.shape[0]:
+            raise RuntimeError("more attention layers ran than the graph was sized for")
+        if self.seq_lens is None:
+            self.seq_lens, self.n_new, self.frame_tokens = list(seq_lens), n_new, frame_tokens
+        elif list(seq_lens) != self.seq_lens:
+            raise RuntimeError("layers disagree on the attention lengths; step cannot be recorded")
+        self.layers.append((attn_module, kv_cache))
+        rows = len(dst)
+        self.host[i] = torch.tensor([start_frames, dst, state.global_end[:rows], state.local_end[:rows]],
+                                    dtype=torch.int64)
+        return self.params_dev[i]
+
+
+class _Recorded:
+    __slots__ = ("graph", "layers", "seq_lens", "n_new", "frame_tokens", "outputs", "launch_counts", "launch_work")
+
+
+class StepGraphs:
+    """Per-pipeline cache of recorded steps, keyed by what the caller says distinguishes them
+    (entry point, block range, shapes)."""
+
+    def __init__(self, device: torch.device, max_layers: int, rows: int):
+        self.device = torch.device(device)
+        self.rows = rows
+        self.params_dev = torch.zeros((max_layers, 4, rows), dtype=torch.int64, device=self.device)
+        self._pinned = [torch.zeros((max_layers, 4, rows), dtype=torch.int64).pin_memory()
+                        for _ in range(_PINNED_SLOTS)]
+        self._pinned_done: List[Optional[torch.cuda.Event]] = [None] * _PINNED_SLOTS
+        self._turn = 0
+        self._graphs: Dict[tuple, _Recorded] = {}
+        self.replays = 0
+        self.eager_steps = 0
+
+    # ------------------------------------------------------------------ host side of a step
+    @staticmethod
+    def steady(layers: Sequence[Tuple[object, dict]], starts: Sequence[int], n_new: int) -> bool:
+        """True when every row of every layer takes the wrapped-cache branch of the slot logic,
+        i.e. attends the whole cache (causal_model.py:301-322), and no layer uses the adaptive
+        sink test.  Nothing is modified."""
+        for module, kv in layers:
+            if module.sink_size > 0 and module.adapt_sink_thr > -1:
+                return False
+            st = RingState.of(kv)
+            smax = kv["k"].shape[1]
+            for i, cs in enumerate(starts):
+                if not (int(cs) + n_new > smax or st.local_end[i] >= smax):
+                    return False
+        return True
+
+    def _stage_params(self, rec: _Recorded, starts: Sequence[int]) -> None:
+        """Advance every layer's slot state by one chunk (as the eager forward would) and send
+        the resulting parameters to the device array, ordered before the replay."""
+        slot = self._turn % _PINNED_SLOTS
+        self._turn += 1
+        done = self._pinned_done[slot]
+        if done is not None:
+            done.synchronize()                 # the copy that last read this staging buffer
+        host = self._pinned[slot]
+        ft = rec.frame_tokens
+        start_frames = [int(s) // ft for s in starts]
+        rows = len(starts)
+        flat: List[List[int]] = []
+        for module, kv in rec.layers:
+            st = RingState.of(kv)
+            dst, lens = st.plan(kv, module, starts, rec.n_new, ft)
+            if lens != rec.seq_lens:
+                raise RuntimeError("slot state left the recorded steady state during a replayed step")
+            flat.append(start_frames + dst + st.global_end[:rows] + st.local_end[:rows])
+        n = len(flat)
+        host[:n] = torch.tensor(flat, dtype=torch.int64).view(n, 4, rows)
+        self.params_dev[:n].copy_(host[:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pinned_done[slot] = ev
+
+    # ------------------------------------------------------------------ record / replay
+    def run(self, key: tuple, fn: Callable[[], object], layers_hint: Sequence[Tuple[object, dict]],
+            starts: Sequence[int], n_new: int, allow_record: bool = True):
+        """Run `fn` (a forward whose tensor arguments all live at fixed addresses) for a chunk whose
+        rows start at `starts`: replayed from the graph recorded under `key` when the step is in
+        steady state, recorded first if there is none yet, eagerly otherwise.  Recording
+        synchronises the device, so a caller with transfers in flight that a peer must complete
+        passes allow_record=False until it is quiescent.  Returns fn's result; for a graph step
+        these are the graph's own output tensors, overwritten by the next replay."""
+        rec = self._graphs.get(key)
+        if (rec is None and not allow_record) or not self.steady(layers_hint, starts, n_new):
+            self.eager_steps += 1
+            return fn()
+        if rec is None:
+            rec = self._record(key, fn, starts)
+        else:
+            self._stage_params(rec, starts)
+        rec.graph.replay()
+        self.replays += 1
+        log = ops.current_launch_log()
+        if log is not None:
+            for name, c in rec.launch_counts.items():
+                log.counts[name] = log.counts.get(name, 0) + c
+                log.work[name] = log.work.get(name, 0.0) + rec.launch_work[name]
+        return rec.outputs
+
+    def _record(self, key: tuple, fn: Callable[[], object], starts: Sequence[int]) -> _Recorded:
+        slot = self._turn % _PINNED_SLOTS
+        self._turn += 1
+        done = self._pinned_done[slot]
+        if done is not None:
+            done.synchronize()
+        recorder = _Recorder(self.params_dev, self._pinned[slot])
+        graph = torch.cuda.CUDAGraph()
+        counter = ops.LaunchLog(timed=False)
+        outer = ops.current_launch_log()
+        ops.set_launch_log(counter)
+        CA.set_step_recorder(recorder)
+        try:
+            # thread_local: other threads (a process group's watchdog) may touch the CUDA API
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                outputs = fn()
+        finally:
+            CA.set_step_recorder(None)
+            ops.set_launch_log(outer)
+        if not recorder.layers:
+            raise RuntimeError("the recorded forward ran no cached attention layer")
+        rec = _Recorded()
+        rec.graph, rec.layers, rec.seq_lens = graph, recorder.layers, recorder.seq_lens
+        rec.n_new, rec.frame_tokens, rec.outputs = recorder.n_new, recorder.frame_tokens, outputs
+        rec.launch_counts, rec.launch_work = dict(counter.counts), dict(counter.work)
+        n = len(rec.layers)
+        # the capture pass already advanced the slot state for this step and filled the staging buffer
+        self.params_dev[:n].copy_(self._pinned[slot][:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pinned_done[slot] = ev
+        self._graphs[key] = rec
+        return rec

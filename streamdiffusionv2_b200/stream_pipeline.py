@@ -141,6 +141,34 @@ class StreamPipeline(nn.Module):
         self.conditional_dict = None
         self._starts_host: List[int] = []
         self._ends_host: List[int] = []
+        self.step_graphs = None      # StepGraphs once enable_step_graphs() was called
+        self._graph_in = None
+
+    # ------------------------------------------------------------------ CUDA-graph replay of steady steps
+    def enable_step_graphs(self, enabled: bool = True) -> None:
+        """Replay the DiT forward of steady-state chunk steps from a CUDA graph (step_graph.py).
+        Call after `prepare`.  Results, cache contents and index state are those of the eager path;
+        steps that are not in steady state still run eagerly."""
+        if not enabled:
+            self.step_graphs = None
+            return
+        if self.kv_cache1 is None or self.hidden_states is None:
+            raise RuntimeError("call prepare() first")
+        if self.device.type != "cuda":
+            raise RuntimeError("step graphs need a CUDA device")
+        from .step_graph import StepGraphs
+        self.step_graphs = StepGraphs(self.device, self.num_transformer_blocks, self.hidden_states.shape[0])
+        self._graph_in = torch.empty_like(self.hidden_states)
+
+    def _forward(self, key, fn, blocks: range, allow_record: bool = True):
+        """fn() eagerly, or through the step graphs when they are enabled."""
+        if self.step_graphs is None:
+            return fn(), False
+        layers = [(self.generator.model.blocks[i].self_attn, self.kv_cache1[i]) for i in blocks]
+        n_new = self.hidden_states.shape[1] * self.frame_seq_length
+        before = self.step_graphs.replays
+        out = self.step_graphs.run(key, fn, layers, self._starts_host, n_new, allow_record=allow_record)
+        return out, self.step_graphs.replays != before
 
     # ------------------------------------------------------------------ cache allocation
     def _initialize_kv_cache(self, batch_size, dtype, device):
@@ -264,11 +292,17 @@ class StreamPipeline(nn.Module):
         self._shift_in(noise, current_start, current_end)
         if current_step is not None:
             self.timestep[0] = current_step
-        self.hidden_states = self.generator(
-            noisy_image_or_video=self.hidden_states, conditional_dict=self.conditional_dict,
-            timestep=self.timestep.unsqueeze(1).expand(-1, self.hidden_states.shape[1]),
+        x_in = self.hidden_states
+        if self.step_graphs is not None:             # a recorded forward reads its input at a fixed address
+            self._graph_in.copy_(self.hidden_states)
+            x_in = self._graph_in
+        fn = lambda: self.generator(
+            noisy_image_or_video=x_in, conditional_dict=self.conditional_dict,
+            timestep=self.timestep.unsqueeze(1).expand(-1, x_in.shape[1]),
             kv_cache=self.kv_cache1, crossattn_cache=self.crossattn_cache,
             current_start=HostStarts(self.kv_cache_starts, self._starts_host), current_end=self.kv_cache_ends)
+        out, replayed = self._forward(("stream", tuple(x_in.shape)), fn, range(self.num_transformer_blocks))
+        self.hidden_states = out.clone() if replayed else out    # a graph's output is overwritten by its next replay
         return self._renoise(self.hidden_states)
 
     def inference_wo_batch(self, noise, current_start, current_end, current_step=None):
@@ -296,7 +330,8 @@ class StreamPipeline(nn.Module):
         return denoised
 
     def inference(self, noise, current_start, current_end, current_step, block_mode="input", block_num=None,
-                  patched_x_shape=None, block_x=None, starts_host: Optional[Sequence[int]] = None):
+                  patched_x_shape=None, block_x=None, starts_host: Optional[Sequence[int]] = None,
+                  allow_record: bool = True):
         """One chunk step of one pipeline stage (causal_stream_inference.py:350-420).  'input':
         shift the new chunk in and run the first block range; 'middle'/'output': adopt the
         previous stage's activations, latents and row starts, run this stage's range."""
@@ -326,7 +361,13 @@ class StreamPipeline(nn.Module):
                       current_start=HostStarts(self.kv_cache_starts, self._starts_host),
                       current_end=self.kv_cache_ends, block_mode=block_mode, block_num=block_num,
                       patched_x_shape=patched_x_shape, block_x=self.block_x)
+        rng = [int(i) for i in (block_num.tolist() if isinstance(block_num, torch.Tensor) else block_num)]
+        owned = range(rng[0], rng[-1])
+        key = (block_mode, rng[0], rng[-1], tuple(self.hidden_states.shape),
+               tuple(int(i) for i in patched_x_shape) if isinstance(patched_x_shape, (list, tuple)) else None)
         if block_mode == "output":
-            denoised = self.generator.forward_output(noisy_image_or_video=self.hidden_states, **common)
-            return self._renoise(denoised), None
-        return self.generator.forward_input(noisy_image_or_video=self.hidden_states, **common)
+            fn = lambda: self.generator.forward_output(noisy_image_or_video=self.hidden_states, **common)
+            denoised, replayed = self._forward(key, fn, owned, allow_record)
+            return self._renoise(denoised.clone() if replayed else denoised), None
+        fn = lambda: self.generator.forward_input(noisy_image_or_video=self.hidden_states, **common)
+        return self._forward(key, fn, owned, allow_record)[0]
