@@ -48,7 +48,8 @@ constexpr int kBarKvEmpty = 2 + kSlots;        // [kSlots]
 constexpr int kBarSFull = 2 + 2 * kSlots;      // [2]
 constexpr int kBarPFull = kBarSFull + 2;       // [2]
 constexpr int kBarOFull = kBarPFull + 2;       // [2]
-constexpr int kNumBars = kBarOFull + 2;
+constexpr int kBarPHalf = kBarOFull + 2;       // [2] first 64 key columns of P written
+constexpr int kNumBars = kBarPHalf + 2;
 static_assert(kNumBars * 8 + 16 <= 256, "barrier block too small");
 
 constexpr uint32_t kIdescQK = umma_idesc_bf16(kBM, kBN, false, false);
@@ -67,11 +68,14 @@ __device__ __forceinline__ void issue_qk(uint32_t tmem_s, uint32_t sq, uint32_t 
   }
 }
 // O[stage] (+)= P[stage] (128 x 128 bf16 in TMEM, 8 columns per K step) * V_tile (kv x d, MN-major).
-__device__ __forceinline__ void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t sv, bool accumulate) {
+// k_begin..k_end select 16-key steps, so that the first half of a tile can be issued while the
+// softmax warps are still producing the second half of P.
+__device__ __forceinline__ void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t sv, bool accumulate,
+                                         int k_begin = 0, int k_end = 8) {
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
+  for (int k = k_begin; k < k_end; ++k) {
     umma_ts(tmem_o, tmem_p + k * 8, umma_smem_desc(sv + k * 2048, kHalfTile, 1024), kIdescPV,
-            (accumulate || k > 0) ? 1u : 0u);
+            (accumulate || k > k_begin) ? 1u : 0u);
   }
 }
 
@@ -120,6 +124,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(kBarSFull + i), 1);
       mbar_init(bar(kBarPFull + i), kBM);
+      mbar_init(bar(kBarPHalf + i), kBM);
       mbar_init(bar(kBarOFull + i), 1);
     }
     fence_mbar_init();
@@ -191,12 +196,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int it_v = 2 * j + 1, it_k = 2 * j + 2;
         const bool more = j + 1 < n_kv;
         for (int s = 0; s < n_stage && ok; ++s) {
-          ok = mbar_wait(bar(kBarPFull + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
+          ok = mbar_wait(bar(kBarPHalf + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
           if (ok && s == 0)
             ok = mbar_wait(bar(kBarKvFull + it_v % kSlots), (it_v / kSlots) & 1, abort_flag, p.status, WAIT_KV_FULL);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(tO[s], tS[s], slot_addr(it_v), j > 0);
+          issue_pv(tO[s], tS[s], slot_addr(it_v), j > 0, 0, 4);
+          ok = mbar_wait(bar(kBarPFull + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(tO[s], tS[s], slot_addr(it_v), true, 4, 8);
           if (s == n_stage - 1) umma_commit(bar(kBarKvEmpty + it_v % kSlots));
           if (more) {
             if (s == 0) {
@@ -288,6 +297,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             pk[i] = pack_bf16x2(p0, p1);
           }
           tmem_st16(tS + c * 16, pk);
+          if (c == 1) {  // the first 64 keys of P are complete: their share of P V can start
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(kBarPHalf + stage));
+          }
         }
         tmem_wait_st();
         tc_fence_before();
