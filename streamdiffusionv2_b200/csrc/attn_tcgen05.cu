@@ -192,34 +192,56 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(bar(kBarSFull + s));
       }
       if (ok) umma_commit(bar(kBarKvEmpty + 0));
+      // ring position (slot, phase parity) of V_j and K_{j+1}, advanced by two items per key tile
+      int slot_v = 1 % kSlots, par_v = 0, slot_k = 2 % kSlots, par_k = 0;
+      auto advance = [](int& slot, int& par) {
+        slot += 2;
+        if (slot >= kSlots) {
+          slot -= kSlots;
+          par ^= 1;
+        }
+      };
+      auto slot_base = [&](int slot) { return base + kSmemKV + slot * kTileBytes; };
+      bool v_ready = false, k_ready = false;  // already seen complete by an early probe
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int it_v = 2 * j + 1, it_k = 2 * j + 2;
         const bool more = j + 1 < n_kv;
+        bool v_next = false, k_next = false;
         for (int s = 0; s < n_stage && ok; ++s) {
           ok = mbar_wait(bar(kBarPHalf + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
-          if (ok && s == 0)
-            ok = mbar_wait(bar(kBarKvFull + it_v % kSlots), (it_v / kSlots) & 1, abort_flag, p.status, WAIT_KV_FULL);
+          if (ok && s == 0 && !v_ready)
+            ok = mbar_wait(bar(kBarKvFull + slot_v), par_v, abort_flag, p.status, WAIT_KV_FULL);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(tO[s], tS[s], slot_addr(it_v), j > 0, 0, 4);
+          issue_pv(tO[s], tS[s], slot_base(slot_v), j > 0, 0, 4);
           ok = mbar_wait(bar(kBarPFull + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
+          if (ok && s == 0 && more && !k_ready)   // before the batch, so that its 12 MMAs go out back to back
+            ok = mbar_wait(bar(kBarKvFull + slot_k), par_k, abort_flag, p.status, WAIT_KV_FULL);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(tO[s], tS[s], slot_addr(it_v), true, 4, 8);
-          if (s == n_stage - 1) umma_commit(bar(kBarKvEmpty + it_v % kSlots));
+          issue_pv(tO[s], tS[s], slot_base(slot_v), true, 4, 8);
           if (more) {
-            if (s == 0) {
-              ok = mbar_wait(bar(kBarKvFull + it_k % kSlots), (it_k / kSlots) & 1, abort_flag, p.status, WAIT_KV_FULL);
-              if (!ok) break;
-              tc_fence_after();
-            }
-            issue_qk(tS[s], sq[s], slot_addr(it_k));
+            issue_qk(tS[s], sq[s], slot_base(slot_k));
             umma_commit(bar(kBarSFull + s));
-            if (s == n_stage - 1) umma_commit(bar(kBarKvEmpty + it_k % kSlots));
           } else {
             umma_commit(bar(kBarOFull + s));
           }
+          if (s == n_stage - 1) {
+            umma_commit(bar(kBarKvEmpty + slot_v));
+            if (more) umma_commit(bar(kBarKvEmpty + slot_k));
+          }
+          if (s == 0 && more) {
+            // this tile's MMAs are queued: probe the next tile's operands while they run
+            int sv = slot_v, pv = par_v, sk = slot_k, pk = par_k;
+            advance(sv, pv);
+            advance(sk, pk);
+            v_next = mbar_test_wait(bar(kBarKvFull + sv), pv);
+            k_next = j + 2 < n_kv && mbar_test_wait(bar(kBarKvFull + sk), pk);
+          }
         }
+        advance(slot_v, par_v);
+        advance(slot_k, par_k);
+        v_ready = v_next;
+        k_ready = k_next;
       }
     }
   } else if (warp >= 4) {
