@@ -306,12 +306,14 @@ def run_single_gpu(args):
         sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        torch.cuda.nvtx.range_push("timed")        # lets a profiler select the launches of the timed region
         e0.record()
         for i in range(args.steps):
             cs, ce = sched.next()
             pipe.inference_stream(dev_chunks[i % n_host], cs, ce)
         e1.record()
         torch.cuda.synchronize()
+        torch.cuda.nvtx.range_pop()
         clocks = sampler.stop()
         ops.set_launch_log(None)
         ms = e0.elapsed_time(e1)
