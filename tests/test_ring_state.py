@@ -56,3 +56,41 @@ def test_slot_outside_cache_raises():
     mod.evict_idx = [[6]]          # a queue entry smaller than the chunk: slot would start at -6
     with pytest.raises(RuntimeError, match="outside"):
         RingState.of(kv).plan(kv, mod, [24], 12, 6)
+
+
+def test_step_graph_steady_state_predicate_matches_the_slot_logic():
+    """StepGraphs.steady must say "every row attends the whole cache" exactly when the slot logic
+    then takes its wrapped branch for every row, and must not modify any state."""
+    import copy
+
+    import torch
+
+    from streamdiffusionv2_b200.ring_state import RingState
+    from streamdiffusionv2_b200.step_graph import StepGraphs
+
+    class Mod:
+        sink_size, adapt_sink_thr, evict_idx = 1, -1, None
+
+    fs, frames, cache_frames, rows = 6, 2, 7, 2
+    n_new, smax = frames * fs, cache_frames * fs
+    mod = Mod()
+    kv = {"k": torch.zeros(rows, smax, 1, 8), "v": torch.zeros(rows, smax, 1, 8),
+          "global_end_index": torch.zeros(rows, dtype=torch.long),
+          "local_end_index": torch.zeros(rows, dtype=torch.long), "total_steps": 2, "current_step": 2}
+    start, history, seen_steady = 0, [0] * rows, 0
+    for step in range(14):
+        history = [start] + history[:-1]
+        st = RingState.of(kv)
+        before = (copy.deepcopy(st.global_end), copy.deepcopy(st.local_end), copy.deepcopy(mod.evict_idx))
+        steady = StepGraphs.steady([(mod, kv)], history, n_new)
+        assert (st.global_end, st.local_end, mod.evict_idx) == before
+        _, lens = st.plan(kv, mod, history, n_new, fs)
+        if steady:                                  # a recorded step attends the whole cache in every row
+            assert all(le == smax for le in lens), (step, lens)
+        elif step > 6:
+            assert False, "a stream that has wrapped must be reported steady"
+        seen_steady += steady
+        start += n_new
+    assert seen_steady >= 8
+    mod.adapt_sink_thr = 0.5                      # the adaptive sink test reads the device: never recorded
+    assert not StepGraphs.steady([(mod, kv)], history, n_new)
