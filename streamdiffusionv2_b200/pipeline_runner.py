@@ -24,6 +24,14 @@ from .stage_transport import StageLink, StagePacket, contiguous_block_ranges
 from .stream_pipeline import StreamPipeline, assign_ints
 
 
+class StreamRestart(Exception):
+    """Raised by `step()` on a stage that received the restart packet; carries the new prompt."""
+
+    def __init__(self, prompt: str):
+        super().__init__("stream restart")
+        self.prompt = prompt
+
+
 class PipelineStageRunner:
     def __init__(self, pipe: StreamPipeline, link: StageLink, rank: int, world_size: int,
                  block_ranges: Optional[Sequence[Sequence[int]]] = None, prefetch: bool = False):
@@ -82,6 +90,15 @@ class PipelineStageRunner:
             return None
 
         pkt: StagePacket = link.recv()
+        if pkt.chunk_idx == -1:
+            # restart (inference_pipe.py:473-493): pass it on, forget the stream's position; the caller
+            # prepares the pipeline again with the new prompt.  Nothing returns to stage 0 for it.
+            if self.role == "middle":
+                link.send_restart(pkt.prompt or "")
+            link.drain()
+            self.items = 0
+            self._quiet = True
+            raise StreamRestart(pkt.prompt or "")
         if self.prefetch and not last:
             link.post_recv()
         step = None if pkt.current_step < 0 else pkt.current_step
@@ -121,6 +138,21 @@ class PipelineStageRunner:
                 self._returned.append(StagePacket(pkt.chunk_idx, pkt.current_step, pkt.patched_x_shape, pkt.starts,
                                                   pkt.ends, None, pkt.latents.clone()))
         self.link.drain()
+        self._quiet = True
+
+    def restart(self, prompt: str) -> None:
+        """Stage 0: start the stream over with a new prompt (inference_pipe.py:448-472).  Takes in and
+        discards what is still travelling back, sends the restart packet down the ring and resets the
+        chunk counters; every other stage's next `step()` raises `StreamRestart(prompt)`."""
+        if self.role != "input":
+            raise RuntimeError("only stage 0 starts a restart")
+        while self.received < self.items:
+            self.link.recv()
+            self.received += 1
+        self._returned.clear()
+        self.link.send_restart(prompt)
+        self.link.drain()
+        self.items = self.received = 0
         self._quiet = True
 
     def park(self) -> None:

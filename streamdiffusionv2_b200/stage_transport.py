@@ -19,8 +19,9 @@ arrives, and measured on B200 that slowed each stage's attention by ~20 % (its C
 SM), while the 20 MB hop itself takes ~30 us.  The closing edge (last stage -> stage 0) carries
 latents only.
 
-`chunk_idx == -1` is kept as the restart sentinel of the reference drivers
-(streamv2v/inference_pipe.py:459-472).
+`chunk_idx == -1` is the restart sentinel of the reference drivers (streamv2v/inference_pipe.py:
+448-493): `send_restart(prompt)` sends a packet whose payload is ignored, followed by the new prompt
+text on the host group; `recv()` returns it with `prompt` set.
 
 Works on CPU tensors with the gloo backend too, which is how the host logic is tested.
 """
@@ -43,6 +44,7 @@ class StagePacket:
     ends: List[int]
     activations: Optional[torch.Tensor]   # [rows, tokens, dim]; None on the closing edge
     latents: torch.Tensor                 # [rows, frames, C, H, W]
+    prompt: Optional[str] = None          # set on a restart packet (chunk_idx == -1)
 
 
 def contiguous_block_ranges(total_blocks: int, world_size: int) -> List[List[int]]:
@@ -175,12 +177,18 @@ class StageLink:
         e.works[i].wait()          # NCCL: makes the current stream wait; gloo: blocks
         e.works[i] = None
         m = e.meta[i].tolist()
+        prompt = None
+        if int(m[0]) == -1:                # restart: the prompt text follows on the host group
+            raw = torch.empty(int(m[1]), dtype=torch.uint8)
+            if raw.numel():
+                dist.recv(raw, src=e.peer, group=e.meta_group)
+            prompt = bytes(raw.tolist()).decode("utf-8")
         buf = e.bufs[i]
         act = buf[:self.act_numel].view(self.act_shape) if self._up_has_act else None
         lat = buf[(self.act_numel if self._up_has_act else 0):].view(self.latent_shape)
         r = self.rows
         return StagePacket(int(m[0]), int(m[1]), [int(x) for x in m[2:7]], [int(x) for x in m[7:7 + r]],
-                           [int(x) for x in m[7 + r:7 + 2 * r]], act, lat)
+                           [int(x) for x in m[7 + r:7 + 2 * r]], act, lat, prompt)
 
     # ------------------------------------------------------------------ send side
     def send(self, chunk_idx: int, activations: Optional[torch.Tensor], latents: torch.Tensor,
@@ -208,6 +216,25 @@ class StageLink:
         e.meta[i].copy_(torch.tensor([chunk_idx, current_step, *patched_x_shape, *starts, *ends], dtype=torch.int64))
         e.meta_works[i] = dist.isend(e.meta[i], dst=e.peer, group=e.meta_group)
         e.works[i] = dist.isend(buf, dst=e.peer, group=e.group)
+
+    def send_restart(self, prompt: str) -> None:
+        """Tell the next stage that the stream starts over with `prompt`.  The packet has the usual
+        fixed-size payload (whatever the send buffer holds; receivers ignore it), `chunk_idx = -1`
+        and the prompt's byte length in the `current_step` field; the text follows."""
+        e = self.down
+        i = e.next
+        e.next = (i + 1) % len(e.bufs)
+        if e.works[i] is not None:
+            e.works[i].wait()
+            e.meta_works[i].wait()
+        data = prompt.encode("utf-8")
+        e.meta[i].zero_()
+        e.meta[i][0] = -1
+        e.meta[i][1] = len(data)
+        e.meta_works[i] = dist.isend(e.meta[i], dst=e.peer, group=e.meta_group)
+        e.works[i] = dist.isend(e.bufs[i], dst=e.peer, group=e.group)
+        if data:
+            dist.send(torch.tensor(list(data), dtype=torch.uint8), dst=e.peer, group=e.meta_group)
 
     def drain(self) -> None:
         """Wait for every outstanding send (call before tearing the process group down)."""

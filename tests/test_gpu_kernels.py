@@ -309,3 +309,14 @@ def test_fused_block_elementwise_match_their_op_chains():
     want = x + (y.unflatten(1, (F, fs)) * gate).flatten(1, 2)
     got = ops.gate_residual(x, y, gate, F)
     assert torch.equal(got, want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,window,chunk", [(2, 4, 1), (3, 8, 3), (1, 21, 2)])
+def test_long_wraparound_run_keeps_device_index_state_equal_to_the_host_mirror(rows, window, chunk):
+    """Hundreds of chunks with the drivers' refresh rule through the append kernel: the device index
+    tensors equal the host mirror at every check and no slot ever leaves the cache (a bad slot is
+    refused by the C ABI and would raise)."""
+    from streamdiffusionv2_b200.kernel_bench import check_index_run
+    res = check_index_run(rows, 2, window, chunk, 400)
+    assert res["mismatches"] == 0, res

@@ -83,6 +83,49 @@ def _worker_pipeline(rank, world, port, ranges, quiesce_every, q, park_at=()):
             dist.destroy_process_group()
 
 
+def _worker_restart(rank, world, port, ranges, q):
+    """3 chunks, a prompt restart from stage 0, 3 more chunks on the same links."""
+    try:
+        _init(rank, world, port)
+        import fake_ops
+        from model_harness import build_pipeline
+        from streamdiffusionv2_b200.pipeline_runner import PipelineStageRunner, StreamRestart
+        from streamdiffusionv2_b200.stage_transport import StageLink
+        fake_ops.install(_Patch())
+        case = cases.MODEL_CASES["m_stages"]
+        fs, sched = cases.model_schedule(case)
+        pipe, first, chunks = build_pipeline(case)
+        role = "input" if rank == 0 else ("output" if rank == world - 1 else "middle")
+        got, outs = [], 0
+        with torch.no_grad():
+            pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
+                         current_start=0, current_end=fs * (1 + case["frames"]), block_mode=role)
+            link = StageLink(rank, world, torch.device("cpu"), (len(case["levels"]), fs * case["frames"],
+                             cases.MODEL_KW["dim"]), tuple(pipe.hidden_states.shape), dtype=torch.float32, timeout_s=60)
+            runner = PipelineStageRunner(pipe, link, rank, world, ranges)
+            i = 0
+            while i < 6:
+                if rank == 0 and i == 3 and not got:
+                    runner.restart("prompt two \u2713")
+                    got.append("sent")
+                noise, (cs, ce) = chunks[i], sched[i]
+                try:
+                    o = runner.step(i, noise, cs, ce, None)
+                except StreamRestart as r:
+                    got.append(r.prompt)
+                    assert runner.items == 0
+                    continue                     # the same chunk index arrives again after the restart
+                outs += o is not None
+                i += 1
+            runner.finish()
+        q.put((rank, "ok", got, outs))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc(), None))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
 def _run(target, world, *args, timeout=240):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -151,6 +194,15 @@ def test_three_rank_ring_parks_and_resumes():
     assert len(parked[2][1]) == len(plain[2][1])
     for a, b in zip(parked[2][1], plain[2][1]):
         assert np.array_equal(a, b)
+
+
+def test_prompt_restart_travels_the_ring_and_the_links_stay_usable():
+    res = _run(_worker_restart, 3, [[0, 1], [1, 2], [2, 3]])
+    for r, v in res.items():
+        assert v[0] == "ok", v[1]
+    assert res[0][1] == ["sent"]
+    assert res[1][1] == ["prompt two \u2713"] and res[2][1] == ["prompt two \u2713"]
+    assert res[2][2] == 6 and res[0][2] == 0
 
 
 def test_three_rank_pipeline_runs_with_a_middle_stage():
