@@ -9,5 +9,7 @@ Public surface:
 from . import _native  # noqa: F401
 from . import ops  # noqa: F401
 from .ring_state import RingState  # noqa: F401
+from .causal_attention import install  # noqa: F401
+from .wan_model import CausalWanModel  # noqa: F401
 
-__all__ = ["ops", "RingState"]
+__all__ = ["ops", "RingState", "install", "CausalWanModel"]
