@@ -140,15 +140,7 @@ class DiTBlock(nn.Module):
                            kv_cache, current_start, None)
         x = add_gated(x, y, gate_a)
         x = x + self.cross_attn(self.norm3(x), context, None, crossattn_cache=crossattn_cache)
-        h = norm_modulate(self.norm2, x, scale_f, shift_f)
-        if fused and self.ffn[0].bias is not None:
-            # first FFN GEMM with bias and tanh-GELU in the GEMM's epilogue (one library call instead of
-            # a GEMM and an element-wise pass over [tokens, ffn_dim]); GELU then sees the fp32 accumulator
-            # instead of its bf16 rounding, which is the only numerical difference to the op chain
-            h = torch._addmm_activation(self.ffn[0].bias, h.flatten(0, 1), self.ffn[0].weight.t(), use_gelu=True)
-            y = self.ffn[2](h).unflatten(0, x.shape[:2])
-        else:
-            y = self.ffn(h)
+        y = self.ffn(norm_modulate(self.norm2, x, scale_f, shift_f))
         return add_gated(x, y, gate_f)
 
 

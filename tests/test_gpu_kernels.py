@@ -320,23 +320,3 @@ def test_long_wraparound_run_keeps_device_index_state_equal_to_the_host_mirror(r
     from streamdiffusionv2_b200.kernel_bench import check_index_run
     res = check_index_run(rows, 2, window, chunk, 400)
     assert res["mismatches"] == 0, res
-
-
-def test_ffn_gelu_epilogue_is_the_tanh_form_the_model_uses():
-    """DiTBlock folds the first FFN GEMM's bias and GELU into the GEMM call on CUDA bf16.  On CUDA that
-    epilogue must be the tanh approximation (the model's nn.GELU(approximate='tanh')); in fp32 the two
-    forms differ by ~5e-4, far more than the epilogue's own error."""
-    g = torch.Generator().manual_seed(5)
-    x = torch.randn(256, 128, generator=g).cuda()
-    w = (torch.randn(512, 128, generator=g) / 8).cuda()
-    b = torch.randn(512, generator=g).cuda()
-    lin = torch.nn.functional.linear(x, w, b)
-    out = torch._addmm_activation(b, x, w.t(), use_gelu=True)
-    d_tanh = (out - torch.nn.functional.gelu(lin, approximate="tanh")).abs().max().item()
-    d_erf = (out - torch.nn.functional.gelu(lin)).abs().max().item()
-    assert d_tanh < 5e-5 and d_erf > 1e-4, (d_tanh, d_erf)
-    xb, wb, bb = x.bfloat16(), w.bfloat16(), b.bfloat16()
-    ref = torch.nn.functional.gelu(torch.nn.functional.linear(xb, wb, bb), approximate="tanh").float()
-    got = torch._addmm_activation(bb, xb, wb.t(), use_gelu=True).float()
-    # three bf16 roundings separate the two (GEMM output, both results): up to 1.5 steps
-    assert ((got - ref).abs() <= 2.0 ** -6 * ref.abs().clamp_min(0.25)).all()
