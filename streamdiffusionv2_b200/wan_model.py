@@ -252,11 +252,19 @@ class CausalWanModel(nn.Module):
         e = self.time_embedding(timestep_features(self.freq_dim, t.flatten()).type_as(x))
         e0 = self.time_projection(e).unflatten(1, (6, self.dim)).unflatten(0, t.shape)
 
-        ctx = context if isinstance(context, torch.Tensor) else torch.stack(
-            [torch.cat([u, u.new_zeros(self.text_len - u.size(0), u.size(1))]) for u in context])
-        if ctx.shape[1] < self.text_len:
-            ctx = torch.cat([ctx, ctx.new_zeros(ctx.shape[0], self.text_len - ctx.shape[1], ctx.shape[2])], dim=1)
-        ctx = self.text_embedding(ctx)
+        # the text embedding only feeds the cross-attention K/V projections, which are skipped once a
+        # block's crossattn_cache is initialised: do not recompute it for blocks that will not read it
+        lo_blk = first if block_mode in ("output", "middle") else 0
+        hi_blk = last if block_mode in ("input", "middle") and 0 <= last <= len(self.blocks) else len(self.blocks)
+        need_ctx = crossattn_cache is None or any(
+            c is None or not c.get("is_init", False) for c in crossattn_cache[lo_blk:hi_blk])
+        ctx = None
+        if need_ctx:
+            ctx = context if isinstance(context, torch.Tensor) else torch.stack(
+                [torch.cat([u, u.new_zeros(self.text_len - u.size(0), u.size(1))]) for u in context])
+            if ctx.shape[1] < self.text_len:
+                ctx = torch.cat([ctx, ctx.new_zeros(ctx.shape[0], self.text_len - ctx.shape[1], ctx.shape[2])], dim=1)
+            ctx = self.text_embedding(ctx)
 
         starts = CA.HostStarts(current_start, CA.host_starts(current_start, bsz)) \
             if isinstance(current_start, torch.Tensor) else current_start
