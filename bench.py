@@ -33,6 +33,9 @@ sys.path.insert(0, ROOT)
 FRAME_TOKENS = 1560          # 30 x 52 tokens per latent frame at 480 x 832
 LATENT_HW = (60, 104)
 CACHE_FRAMES = 21            # 1 sink + 20 ring
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch at the N=1 workload's shape (ncu, B200)
+ATTN_DRAM_BYTES_1P3B = 450.4e6 + 14.5e6
+APPEND_DRAM_BYTES_1P3B = 57.56e6 + 11.5e6
 FRAMES_PER_CHUNK = 2
 VIDEO_FRAMES_PER_CHUNK = 4 * FRAMES_PER_CHUNK
 LEVELS = [700, 500]
@@ -376,14 +379,21 @@ def run_single_gpu(args):
         "gpu_launches": launches, "gpu_launches_by_kernel": log.counts,
         "roofline": {"kernel": "attn_kvcache (tcgen05)", "bound": "tensor", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
-                     "traffic": None, "avg_launch_ms": att_ms, "flops_per_launch": att_flops,
+                     "traffic": ATTN_DRAM_BYTES_1P3B if MODEL_1P3B["dim"] == 1536 else None,
+                     "traffic_note": "DRAM bytes read + written per launch, one ncu capture of this shape "
+                                     "(2 rows x 12 heads x 3120 queries x 32760 keys); algorithmic K+V+Q+out = 441 MB",
+                     "avg_launch_ms": att_ms, "flops_per_launch": att_flops,
                      "share_of_step": att_ms * log.counts["attn_kvcache"] / ms,
                      "timed_in": "launch-by-launch pass of the same steps after the timed region (graph replay "
                                  "hides single launches from events)" if args.graphs else "the timed region"},
         "roofline_append": {"kernel": "rope_kv_append", "bound": "hbm", "achieved": app_bytes / (app_ms * 1e-3) / 1e9,
                             "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": app_bytes / (app_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                            "avg_launch_ms": app_ms, "bytes_per_launch": app_bytes, "traffic": None},
+                            "avg_launch_ms": app_ms, "bytes_per_launch": app_bytes,
+                            "traffic": APPEND_DRAM_BYTES_1P3B if MODEL_1P3B["dim"] == 1536 else None,
+                            "traffic_note": "DRAM bytes per launch, one ncu capture of this shape from a flushed "
+                                            "cache: all 57.5 MB of reads, 11.5 MB of the 57.5 MB of writes (the "
+                                            "rest is still in L2 when the kernel ends)"},
         "cpu_baseline": cpu, "clocks": clocks,
         "step_graphs": None if pipe.step_graphs is None else {"replayed_steps": pipe.step_graphs.replays,
                                                               "eager_steps": pipe.step_graphs.eager_steps},
