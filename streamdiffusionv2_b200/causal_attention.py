@@ -14,6 +14,7 @@ attention runs in the sm_100a kernels.  There is no fallback to PyTorch attentio
 """
 from __future__ import annotations
 
+import inspect
 import math
 import types
 from typing import List, Optional, Sequence
@@ -144,6 +145,22 @@ def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_
     return ops.attn_kvcache_simt(roped_q, kv_cache["k"], kv_cache["v"], seq_lens)
 
 
+def _fusable(x: torch.Tensor) -> bool:
+    """The fused element-wise kernels serve bf16 CUDA tensors with rows of at most 8192 elements."""
+    return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192
+
+
+def _qk_norm(norm, x: torch.Tensor) -> torch.Tensor:
+    """norm(x) for the q / k norms.  An RMS norm with a bf16 weight (the reference's WanRMSNorm,
+    models/wan/wan_base/modules/model.py:69-84, or this package's own) runs as one launch that
+    reproduces its roundings; anything else (Identity when qk_norm is off, fp32 runs) is called as is."""
+    w = getattr(norm, "weight", None)
+    if (w is not None and type(norm).__name__.endswith("RMSNorm") and _fusable(x) and w.dtype == torch.bfloat16
+            and hasattr(norm, "eps")):
+        return ops.rmsnorm(x, w, norm.eps)
+    return norm(x)
+
+
 def self_attention_forward(self, x, seq_lens, grid_sizes, freqs, block_mask, kv_cache=None, current_start=0,
                            current_end=0, causal_rope_cache=None):
     """Drop-in for CausalWanSelfAttention.forward on the kv-cache path (the training branch, which
@@ -154,8 +171,8 @@ def self_attention_forward(self, x, seq_lens, grid_sizes, freqs, block_mask, kv_
             raise RuntimeError("the kernel-backed self-attention serves the kv-cache path only")
         return original(x, seq_lens, grid_sizes, freqs, block_mask)
     b, s, n, d = *x.shape[:2], self.num_heads, self.head_dim
-    q = self.norm_q(self.q(x)).view(b, s, n, d)
-    k = self.norm_k(self.k(x)).view(b, s, n, d)
+    q = _qk_norm(self.norm_q, self.q(x)).view(b, s, n, d)
+    k = _qk_norm(self.norm_k, self.k(x)).view(b, s, n, d)
     v = self.v(x).view(b, s, n, d)
     out = cached_attention(self, q, k, v, grid_sizes, freqs, kv_cache, current_start)
     return self.o(out.flatten(2))
@@ -165,11 +182,11 @@ def cross_attention_forward(self, x, context, context_lens, crossattn_cache=None
     """Drop-in for WanT2VCrossAttention.forward: K/V of the text context are computed on the
     first call after `is_init` was cleared and read from the cache afterwards."""
     b, n, d = x.size(0), self.num_heads, self.head_dim
-    q = self.norm_q(self.q(x)).view(b, -1, n, d)
+    q = _qk_norm(self.norm_q, self.q(x)).view(b, -1, n, d)
     if crossattn_cache is not None:
         if not crossattn_cache["is_init"]:
             crossattn_cache["is_init"] = True
-            k = self.norm_k(self.k(context)).view(b, -1, n, d)
+            k = _qk_norm(self.norm_k, self.k(context)).view(b, -1, n, d)
             v = self.v(context).view(b, -1, n, d)
             crossattn_cache["k"] = k
             crossattn_cache["v"] = v
@@ -188,14 +205,52 @@ def cross_attention_forward(self, x, context, context_lens, crossattn_cache=None
     return self.o(out.flatten(2))
 
 
-def install(model) -> int:
+def block_forward(self, x, e, seq_lens, grid_sizes, freqs, context, context_lens, block_mask, kv_cache=None,
+                  crossattn_cache=None, current_start=0, current_end=0, causal_rope_cache=None):
+    """Drop-in for CausalWanAttentionBlock.forward (models/wan/causal_model.py:432-483): same
+    arguments, same arithmetic.  On bf16 CUDA tensors the two norm -> modulate chains and the two
+    gated residual additions run as one launch each (they reproduce the op chain's bf16 roundings);
+    otherwise the op chain itself runs.  x [B, L, C]; e [B, F, 6, C]."""
+    frames = e.shape[1]
+    per_frame = x.shape[1] // frames
+    shift_a, scale_a, gate_a, shift_f, scale_f, gate_f = (self.modulation.unsqueeze(1) + e).chunk(6, dim=2)
+    fused = _fusable(x) and shift_a.dtype == torch.bfloat16
+
+    def norm_modulate(norm, y, scale, shift):
+        if fused and getattr(norm, "weight", None) is None:
+            return ops.ln_modulate(y, scale, shift, frames, norm.eps)
+        return (norm(y).unflatten(1, (frames, per_frame)) * (1 + scale) + shift).flatten(1, 2)
+
+    def add_gated(x, y, gate):
+        if fused:
+            return ops.gate_residual(x, y, gate, frames)
+        return x + (y.unflatten(1, (frames, per_frame)) * gate).flatten(1, 2)
+
+    y = self.self_attn(norm_modulate(self.norm1, x, scale_a, shift_a), seq_lens, grid_sizes, freqs, block_mask,
+                       kv_cache, current_start, current_end, causal_rope_cache)
+    x = add_gated(x, y, gate_a)
+    x = x + self.cross_attn(self.norm3(x), context, context_lens, crossattn_cache=crossattn_cache)
+    y = self.ffn(norm_modulate(self.norm2, x, scale_f, shift_f))
+    return add_gated(x, y, gate_f)
+
+
+def install(model, fuse_block: bool = True) -> int:
     """Bind the kernel-backed forwards onto every block of `model` (anything with a `.blocks`
     list whose items have `.self_attn` and `.cross_attn`, as the reference CausalWanModel has).
     Parameters, buffers and attribute names are left untouched, so checkpoints keep loading.
-    Returns the number of blocks patched."""
+    With `fuse_block`, blocks that have the reference block's layout (norm1, norm2, norm3, ffn,
+    modulation) also get `block_forward`, whose element-wise chains are single launches on bf16
+    CUDA tensors.  Returns the number of blocks patched."""
     n = 0
     for block in model.blocks:
         sa, ca = block.self_attn, block.cross_attn
+        takes_reference_args = "context_lens" in inspect.signature(
+            getattr(block, "_sdv2_original_forward", block.forward)).parameters
+        if (fuse_block and takes_reference_args
+                and all(hasattr(block, a) for a in ("norm1", "norm2", "norm3", "ffn", "modulation"))):
+            if not hasattr(block, "_sdv2_original_forward"):
+                block._sdv2_original_forward = block.forward
+            block.forward = types.MethodType(block_forward, block)
         if not hasattr(sa, "_sdv2_original_forward"):
             sa._sdv2_original_forward = sa.forward
         sa.forward = types.MethodType(self_attention_forward, sa)

@@ -320,3 +320,45 @@ def test_long_wraparound_run_keeps_device_index_state_equal_to_the_host_mirror(r
     from streamdiffusionv2_b200.kernel_bench import check_index_run
     res = check_index_run(rows, 2, window, chunk, 400)
     assert res["mismatches"] == 0, res
+
+
+def test_block_forward_with_reference_arguments_equals_the_block_it_replaces():
+    """`install()` binds `block_forward` (the reference block's argument list) onto reference blocks.
+    Here it runs on one of this package's blocks, on CUDA bf16 so that the fused launches are taken,
+    against that block's own forward on the same inputs and cache state."""
+    import copy
+    import types
+
+    from streamdiffusionv2_b200 import causal_attention as CA
+    from streamdiffusionv2_b200.wan_model import DiTBlock, build_rope_table
+    torch.manual_seed(3)
+    dim, heads, fs, frames, rows = 256, 2, 6, 2, 2
+    blk = DiTBlock(dim, 512, heads, qk_norm=True, cross_attn_norm=True).cuda().to(torch.bfloat16).eval()
+    blk.self_attn.sink_size, blk.self_attn.adapt_sink_thr = 1, -1
+    x = torch.randn(rows, frames * fs, dim).cuda().bfloat16()
+    e = torch.randn(rows, frames, 6, dim).cuda().bfloat16()
+    ctx = torch.randn(rows, 512, dim).cuda().bfloat16()
+    freqs = build_rope_table(128)
+    grid = torch.tensor([[frames, 2, 3]] * rows)
+
+    def caches():
+        kv = {"k": torch.zeros(rows, 8 * fs, heads, 128, device="cuda", dtype=torch.bfloat16),
+              "v": torch.zeros(rows, 8 * fs, heads, 128, device="cuda", dtype=torch.bfloat16),
+              "global_end_index": torch.zeros(rows, dtype=torch.long, device="cuda"),
+              "local_end_index": torch.zeros(rows, dtype=torch.long, device="cuda"), "total_steps": 2, "current_step": 2}
+        return kv, {"k": None, "v": None, "is_init": False}
+
+    outs = []
+    with torch.no_grad():
+        for use_adapter in (False, True):
+            b2 = copy.deepcopy(blk)
+            b2.self_attn.evict_idx = None
+            kv, cc = caches()
+            starts = CA.HostStarts(torch.zeros(rows, dtype=torch.long, device="cuda"), [0] * rows)
+            if use_adapter:
+                fwd = types.MethodType(CA.block_forward, b2)
+                outs.append((fwd(x, e, None, grid, freqs, ctx, None, None, kv, cc, starts, None), kv))
+            else:
+                outs.append((b2(x, e, grid, freqs, ctx, kv, cc, starts), kv))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1]["k"], outs[1][1]["k"]) and torch.equal(outs[0][1]["v"], outs[1][1]["v"])
