@@ -411,7 +411,7 @@ def run_pipeline(args):
     import torch.distributed as dist
     from streamdiffusionv2_b200 import ops
     from streamdiffusionv2_b200.pipeline_runner import PipelineStageRunner
-    from streamdiffusionv2_b200.stage_transport import StageLink, contiguous_block_ranges
+    from streamdiffusionv2_b200.stage_transport import StageLink, balanced_block_ranges, contiguous_block_ranges
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -420,7 +420,8 @@ def run_pipeline(args):
     dist.init_process_group("nccl")   # lazy communicators: the stage links create theirs one edge at a time
     peaks = measured_peaks()
     pipe = build_pipeline(device)
-    ranges = contiguous_block_ranges(MODEL_1P3B["num_layers"], world)
+    split = balanced_block_ranges if args.block_split == "balanced" else contiguous_block_ranges
+    ranges = split(MODEL_1P3B["num_layers"], world)
     role = "input" if rank == 0 else ("output" if rank == world - 1 else "middle")
     g = torch.Generator(device="cpu").manual_seed(2)
     h, w = LATENT_HW
@@ -558,6 +559,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graphs", dest="graphs", action="store_false",
                     help="launch every op of every step from Python instead of replaying steady steps from a CUDA graph")
+    ap.add_argument("--block-split", default="reference", choices=["reference", "balanced"],
+                    help="N>1: the reference's default block ranges (remainder on the first stages) or the "
+                         "remainder on the middle stages")
     ap.add_argument("--model", default="1.3b", choices=["1.3b", "14b"],
                     help="1.3b is the headline workload; 14b = 40 blocks, dim 5120, 40 heads, 4 denoise levels")
     args = ap.parse_args()

@@ -65,6 +65,26 @@ def contiguous_block_ranges(total_blocks: int, world_size: int) -> List[List[int
     return out
 
 
+def balanced_block_ranges(total_blocks: int, world_size: int) -> List[List[int]]:
+    """Contiguous ranges with the remainder on the stages in the middle: the first stage also embeds
+    the latents and shifts the stream batch, the last one runs the head, the x0 conversion and the
+    re-noising, so giving them the extra blocks (as the default split does) makes them the slowest.
+    Same block counts as `contiguous_block_ranges` up to which stages hold the remainder; this is the
+    split the reference's run-time rebalancing (streamv2v/inference_pipe.py:802-843) moves towards."""
+    base, rem = divmod(total_blocks, world_size)
+    sizes = [base] * world_size
+    # innermost stages first; of two equally far from the middle, the later one (the first stage's extra
+    # work was measured larger than the last stage's)
+    order = sorted(range(world_size), key=lambda r: (abs(r - (world_size - 1) / 2), -r))
+    for r in order[:rem]:
+        sizes[r] += 1
+    out, start = [], 0
+    for n in sizes:
+        out.append([start, start + n])
+        start += n
+    return out
+
+
 class _Edge:
     """One direction of one ring edge as seen from this rank."""
 

@@ -287,6 +287,17 @@ def test_wrong_shape_is_rejected_before_anything_is_sent():
     assert res[0][0] == "raised", res[0]
 
 
+def test_balanced_block_ranges_cover_all_blocks_and_spare_the_end_stages():
+    from streamdiffusionv2_b200.stage_transport import balanced_block_ranges, contiguous_block_ranges
+    for total, world in ((30, 8), (30, 4), (30, 2), (40, 8), (30, 7), (3, 3), (31, 4)):
+        r = balanced_block_ranges(total, world)
+        assert r[0][0] == 0 and r[-1][1] == total and all(a[1] == b[0] for a, b in zip(r, r[1:]))
+        sizes = [b - a for a, b in r]
+        assert sorted(sizes) == sorted(b - a for a, b in contiguous_block_ranges(total, world)) or world == 2
+        assert sizes[0] == min(sizes) and sizes[-1] <= sizes[len(sizes) // 2]
+    assert [b - a for a, b in balanced_block_ranges(30, 8)] == [3, 4, 4, 4, 4, 4, 4, 3]
+
+
 def test_block_ranges_follow_the_reference_split():
     from streamdiffusionv2_b200.stage_transport import contiguous_block_ranges as r
     assert r(30, 2) == [[0, 15], [15, 30]]
