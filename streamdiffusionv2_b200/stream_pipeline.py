@@ -147,8 +147,10 @@ class StreamPipeline(nn.Module):
     # ------------------------------------------------------------------ CUDA-graph replay of steady steps
     def enable_step_graphs(self, enabled: bool = True) -> None:
         """Replay the DiT forward of steady-state chunk steps from a CUDA graph (step_graph.py).
-        Call after `prepare`.  Results, cache contents and index state are those of the eager path;
-        steps that are not in steady state still run eagerly."""
+        Call after `prepare`, and again after every later `prepare` (a new prompt or stream replaces
+        the tensors a recorded step points at, so `prepare` drops the recordings).  Results, cache
+        contents and index state are those of the eager path; steps that are not in steady state
+        still run eagerly."""
         if not enabled:
             self.step_graphs = None
             return
@@ -203,6 +205,8 @@ class StreamPipeline(nn.Module):
         others are moved to host memory as the reference does (`unowned="cpu"`) or released
         (`unowned="free"`)."""
         self.device = torch.device(device)
+        # recorded steps hold the addresses of the caches and of the text K/V that this call replaces
+        self.step_graphs, self._graph_in = None, None
         batch_size = noise.shape[0]
         self.conditional_dict = self.text_encoder(text_prompts=text_prompts)
         if self.kv_cache1 is None:
