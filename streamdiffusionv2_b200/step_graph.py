@@ -52,7 +52,17 @@ class _Recorder:
 
 
 class _Recorded:
-    __slots__ = ("graph", "layers", "seq_lens", "n_new", "frame_tokens", "outputs", "launch_counts", "launch_work")
+    __slots__ = ("graph", "layers", "seq_lens", "n_new", "frame_tokens", "outputs", "launch_counts", "launch_work",
+                 "pointers")
+
+
+def _cache_pointers(layers: Sequence[Tuple[object, dict]]) -> List[int]:
+    """Addresses a recorded step has baked in for these layers' caches."""
+    out: List[int] = []
+    for _, kv in layers:
+        out += [kv["k"].data_ptr(), kv["v"].data_ptr(), kv["global_end_index"].data_ptr(),
+                kv["local_end_index"].data_ptr()]
+    return out
 
 
 class StepGraphs:
@@ -123,6 +133,9 @@ class StepGraphs:
         passes allow_record=False until it is quiescent.  Returns fn's result; for a graph step
         these are the graph's own output tensors, overwritten by the next replay."""
         rec = self._graphs.get(key)
+        if rec is not None and rec.pointers != _cache_pointers(rec.layers):
+            del self._graphs[key]          # somebody replaced a cache tensor: the recording is stale
+            rec = None
         if (rec is None and not allow_record) or not self.steady(layers_hint, starts, n_new):
             self.eager_steps += 1
             return fn()
@@ -164,6 +177,7 @@ class StepGraphs:
         rec.graph, rec.layers, rec.seq_lens = graph, recorder.layers, recorder.seq_lens
         rec.n_new, rec.frame_tokens, rec.outputs = recorder.n_new, recorder.frame_tokens, outputs
         rec.launch_counts, rec.launch_work = dict(counter.counts), dict(counter.work)
+        rec.pointers = _cache_pointers(rec.layers)
         n = len(rec.layers)
         # the capture pass already advanced the slot state for this step and filled the staging buffer
         self.params_dev[:n].copy_(self._pinned[slot][:n], non_blocking=True)
