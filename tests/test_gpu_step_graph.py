@@ -66,7 +66,7 @@ def test_indirect_append_refuses_out_of_range_device_parameters(bad):
     ops.read_status(dev)     # the report was cleared
 
 
-def _run_stream(case_name, graphs):
+def _run_stream(case_name, graphs, swap_at=None):
     from model_harness import build_pipeline, snapshot
     case = cases.MODEL_CASES[case_name]
     fs, sched = cases.model_schedule(case)
@@ -79,7 +79,10 @@ def _run_stream(case_name, graphs):
         if graphs:
             pipe.enable_step_graphs()
         torch.manual_seed(12)
-        for noise, (cs, ce) in zip(chunks, sched):
+        for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
+            if i == swap_at:          # what a cache manager does: same contents, new tensors
+                for kv in pipe.kv_cache1:
+                    kv["k"], kv["v"] = kv["k"].clone(), kv["v"].clone()
             outs.append(pipe.inference_stream(noise, cs, ce).clone())
     torch.cuda.synchronize()
     n_layers = cases.MODEL_KW["num_layers"]
@@ -93,6 +96,15 @@ def test_graph_replayed_stream_equals_the_eager_stream():
     ops.read_status(torch.device("cuda"))
     sg = pipe.step_graphs
     assert sg.replays >= 5 and sg.eager_steps >= 1, (sg.replays, sg.eager_steps)   # the fill steps run eagerly
+    for i, (a, b) in enumerate(zip(eager_out, graph_out)):
+        assert torch.equal(a, b), f"chunk {i}"
+    assert eager_state == graph_state
+
+
+def test_replaced_cache_tensors_invalidate_the_recording():
+    eager_out, eager_state, _ = _run_stream("m_stream", graphs=False, swap_at=6)
+    graph_out, graph_state, pipe = _run_stream("m_stream", graphs=True, swap_at=6)
+    assert pipe.step_graphs.replays >= 4
     for i, (a, b) in enumerate(zip(eager_out, graph_out)):
         assert torch.equal(a, b), f"chunk {i}"
     assert eager_state == graph_state
