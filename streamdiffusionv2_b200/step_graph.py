@@ -56,12 +56,16 @@ class _Recorded:
                  "pointers")
 
 
-def _cache_pointers(layers: Sequence[Tuple[object, dict]]) -> List[int]:
-    """Addresses a recorded step has baked in for these layers' caches."""
+def _cache_pointers(layers: Sequence[tuple]) -> List[int]:
+    """Addresses a recorded step has baked in for these layers: (attention module, kv_cache dict) or
+    (attention module, kv_cache dict, crossattn_cache dict) per layer."""
     out: List[int] = []
-    for _, kv in layers:
+    for entry in layers:
+        kv = entry[1]
         out += [kv["k"].data_ptr(), kv["v"].data_ptr(), kv["global_end_index"].data_ptr(),
                 kv["local_end_index"].data_ptr()]
+        if len(entry) > 2 and entry[2] is not None and entry[2].get("is_init"):
+            out += [entry[2]["k"].data_ptr(), entry[2]["v"].data_ptr()]
     return out
 
 
@@ -83,11 +87,15 @@ class StepGraphs:
 
     # ------------------------------------------------------------------ host side of a step
     @staticmethod
-    def steady(layers: Sequence[Tuple[object, dict]], starts: Sequence[int], n_new: int) -> bool:
+    def steady(layers: Sequence[tuple], starts: Sequence[int], n_new: int) -> bool:
         """True when every row of every layer takes the wrapped-cache branch of the slot logic,
-        i.e. attends the whole cache (causal_model.py:301-322), and no layer uses the adaptive
-        sink test.  Nothing is modified."""
-        for module, kv in layers:
+        i.e. attends the whole cache (causal_model.py:301-322), no layer uses the adaptive sink
+        test, and (where the layer's crossattn_cache is given as a third entry) the text K/V are
+        cached, so that the step launches exactly what a recorded one launched.  Nothing is modified."""
+        for entry in layers:
+            module, kv = entry[0], entry[1]
+            if len(entry) > 2 and entry[2] is not None and not entry[2].get("is_init", False):
+                return False
             if module.sink_size > 0 and module.adapt_sink_thr > -1:
                 return False
             st = RingState.of(kv)
@@ -133,7 +141,7 @@ class StepGraphs:
         passes allow_record=False until it is quiescent.  Returns fn's result; for a graph step
         these are the graph's own output tensors, overwritten by the next replay."""
         rec = self._graphs.get(key)
-        if rec is not None and rec.pointers != _cache_pointers(rec.layers):
+        if rec is not None and rec.pointers != _cache_pointers(layers_hint):
             del self._graphs[key]          # somebody replaced a cache tensor: the recording is stale
             rec = None
         if (rec is None and not allow_record) or not self.steady(layers_hint, starts, n_new):
@@ -141,6 +149,7 @@ class StepGraphs:
             return fn()
         if rec is None:
             rec = self._record(key, fn, starts)
+            rec.pointers = _cache_pointers(layers_hint)
         else:
             self._stage_params(rec, starts)
         rec.graph.replay()
@@ -177,7 +186,7 @@ class StepGraphs:
         rec.graph, rec.layers, rec.seq_lens = graph, recorder.layers, recorder.seq_lens
         rec.n_new, rec.frame_tokens, rec.outputs = recorder.n_new, recorder.frame_tokens, outputs
         rec.launch_counts, rec.launch_work = dict(counter.counts), dict(counter.work)
-        rec.pointers = _cache_pointers(rec.layers)
+        rec.pointers = []
         n = len(rec.layers)
         # the capture pass already advanced the slot state for this step and filled the staging buffer
         self.params_dev[:n].copy_(self._pinned[slot][:n], non_blocking=True)

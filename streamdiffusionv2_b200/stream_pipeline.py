@@ -166,7 +166,8 @@ class StreamPipeline(nn.Module):
         """fn() eagerly, or through the step graphs when they are enabled."""
         if self.step_graphs is None:
             return fn(), False
-        layers = [(self.generator.model.blocks[i].self_attn, self.kv_cache1[i]) for i in blocks]
+        layers = [(self.generator.model.blocks[i].self_attn, self.kv_cache1[i], self.crossattn_cache[i])
+                  for i in blocks]
         n_new = self.hidden_states.shape[1] * self.frame_seq_length
         before = self.step_graphs.replays
         out = self.step_graphs.run(key, fn, layers, self._starts_host, n_new, allow_record=allow_record)

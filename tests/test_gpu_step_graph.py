@@ -66,7 +66,7 @@ def test_indirect_append_refuses_out_of_range_device_parameters(bad):
     ops.read_status(dev)     # the report was cleared
 
 
-def _run_stream(case_name, graphs, swap_at=None):
+def _run_stream(case_name, graphs, swap_at=None, reprompt_at=None):
     from model_harness import build_pipeline, snapshot
     case = cases.MODEL_CASES[case_name]
     fs, sched = cases.model_schedule(case)
@@ -83,6 +83,10 @@ def _run_stream(case_name, graphs, swap_at=None):
             if i == swap_at:          # what a cache manager does: same contents, new tensors
                 for kv in pipe.kv_cache1:
                     kv["k"], kv["v"] = kv["k"].clone(), kv["v"].clone()
+            if i == reprompt_at:      # a new prompt mid-stream: the text K/V are recomputed on the next call
+                pipe.conditional_dict["prompt_embeds"] = pipe.conditional_dict["prompt_embeds"].flip(1).contiguous()
+                for cc in pipe.crossattn_cache:
+                    cc["is_init"] = False
             outs.append(pipe.inference_stream(noise, cs, ce).clone())
     torch.cuda.synchronize()
     n_layers = cases.MODEL_KW["num_layers"]
@@ -105,6 +109,16 @@ def test_replaced_cache_tensors_invalidate_the_recording():
     eager_out, eager_state, _ = _run_stream("m_stream", graphs=False, swap_at=6)
     graph_out, graph_state, pipe = _run_stream("m_stream", graphs=True, swap_at=6)
     assert pipe.step_graphs.replays >= 4
+    for i, (a, b) in enumerate(zip(eager_out, graph_out)):
+        assert torch.equal(a, b), f"chunk {i}"
+    assert eager_state == graph_state
+
+
+def test_a_new_prompt_mid_stream_is_not_served_from_a_stale_recording():
+    eager_out, eager_state, _ = _run_stream("m_stream", graphs=False, reprompt_at=6)
+    graph_out, graph_state, pipe = _run_stream("m_stream", graphs=True, reprompt_at=6)
+    plain_out, _, _ = _run_stream("m_stream", graphs=False)
+    assert not torch.equal(plain_out[7], eager_out[7])          # the prompt does change the result
     for i, (a, b) in enumerate(zip(eager_out, graph_out)):
         assert torch.equal(a, b), f"chunk {i}"
     assert eager_state == graph_state
