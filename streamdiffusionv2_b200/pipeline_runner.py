@@ -41,7 +41,8 @@ class PipelineStageRunner:
         self.prefetch = prefetch
         self.pipe, self.link, self.rank, self.world = pipe, link, rank, world_size
         ranges = block_ranges or contiguous_block_ranges(pipe.num_transformer_blocks, world_size)
-        self.block_range = [int(ranges[rank][0]), int(ranges[rank][1])]
+        self.block_ranges = [[int(a), int(b)] for a, b in ranges]     # of every stage
+        self.block_range = list(self.block_ranges[rank])
         self.role = "input" if rank == 0 else ("output" if rank == world_size - 1 else "middle")
         self.items = 0            # chunks processed (stage 0: sent)
         self.received = 0         # stage 0: packets taken from the closing edge
@@ -154,6 +155,85 @@ class PipelineStageRunner:
         self.link.drain()
         self.items = self.received = 0
         self._quiet = True
+
+    # ------------------------------------------------------------------ moving blocks between stages
+    _QUEUE_SLOTS = 64   # evict-queue entries shipped per row (a queue holds at most one entry per cache frame)
+
+    def rebalance(self, new_ranges: Sequence[Sequence[int]]) -> None:
+        """Switch to new contiguous block ranges and move the K/V state of every block whose owner
+        changes (streamv2v/inference_pipe.py:802-843, communication/kv_cache_manager.py:48-144).
+        Call on every rank with the same ranges, directly after `quiesce()`: with the ring empty all
+        stages have processed the same chunks, so the state moves as it is - K, V, both index
+        tensors, the step counters and the block's evict queue (which the reference leaves behind).
+        The old owner keeps an empty placeholder; recorded step graphs are dropped."""
+        import torch.distributed as dist
+        if not self._quiet:
+            raise RuntimeError("rebalance() needs an empty ring: call quiesce() first")
+        new_ranges = [[int(a), int(b)] for a, b in new_ranges]
+        total = self.pipe.num_transformer_blocks
+        if (len(new_ranges) != self.world or new_ranges[0][0] != 0 or new_ranges[-1][1] != total
+                or any(a[1] != b[0] for a, b in zip(new_ranges, new_ranges[1:]))
+                or any(b <= a for a, b in new_ranges)):
+            raise ValueError("block ranges must be contiguous, non-empty and cover every block")
+
+        def owners(ranges):
+            out = [0] * total
+            for r, (a, b) in enumerate(ranges):
+                out[a:b] = [r] * (b - a)
+            return out
+
+        old_owner, new_owner = owners(self.block_ranges), owners(new_ranges)
+        pipe, dev = self.pipe, self.pipe.device
+        for i in range(total):
+            src, dst = old_owner[i], new_owner[i]
+            if src == dst or self.rank not in (src, dst):
+                continue
+            kv = pipe.kv_cache1[i]
+            module = pipe.generator.model.blocks[i].self_attn
+            if self.rank == src:
+                rows = kv["k"].shape[0]
+                meta = torch.zeros(3 + rows * (1 + self._QUEUE_SLOTS), dtype=torch.int64)
+                meta[0], meta[1], meta[2] = rows, int(kv["current_step"]), int(kv["total_steps"])
+                queues = module.evict_idx if module.evict_idx is not None else []
+                for r in range(rows):
+                    q = [int(x) for x in (queues[r] if r < len(queues) else [])]
+                    if len(q) > self._QUEUE_SLOTS:
+                        raise RuntimeError("evict queue longer than the transfer record")
+                    base = 3 + r * (1 + self._QUEUE_SLOTS)
+                    meta[base] = len(q) if r < len(queues) else -1
+                    meta[base + 1:base + 1 + len(q)] = torch.tensor(q, dtype=torch.int64)
+                for t in (meta.to(dev), kv["global_end_index"], kv["local_end_index"], kv["k"].to(dev),
+                          kv["v"].to(dev)):
+                    dist.send(t.contiguous(), dst=dst)
+                kv["k"], kv["v"] = kv["k"][:, :0], kv["v"][:, :0]         # placeholder, as for never-owned blocks
+                kv.pop("_sdv2_host", None)
+            else:
+                rows = pipe.hidden_states.shape[0]
+                meta = torch.zeros(3 + rows * (1 + self._QUEUE_SLOTS), dtype=torch.int64, device=dev)
+                dist.recv(meta, src=src)
+                m = meta.tolist()
+                if m[0] != rows:
+                    raise RuntimeError("the sender's cache has another number of rows")
+                dtype = pipe.hidden_states.dtype
+                shape = (rows, pipe.kv_cache_length, pipe.num_heads, pipe.head_dim)
+                ge = torch.empty(rows, dtype=torch.int64, device=dev)
+                le = torch.empty(rows, dtype=torch.int64, device=dev)
+                k = torch.empty(shape, dtype=dtype, device=dev)
+                v = torch.empty(shape, dtype=dtype, device=dev)
+                for t in (ge, le, k, v):
+                    dist.recv(t, src=src)
+                kv.update(k=k, v=v, global_end_index=ge, local_end_index=le, current_step=m[1], total_steps=m[2])
+                kv.pop("_sdv2_host", None)            # the host mirror is re-read from the received tensors
+                queues = []
+                for r in range(rows):
+                    base = 3 + r * (1 + self._QUEUE_SLOTS)
+                    if m[base] >= 0:
+                        queues.append([int(x) for x in m[base + 1:base + 1 + m[base]]])
+                module.evict_idx = queues if queues else None
+        self.block_ranges = new_ranges
+        self.block_range = list(new_ranges[self.rank])
+        if pipe.step_graphs is not None:
+            pipe.step_graphs.forget()
 
     def park(self) -> None:
         """Pause with the ring still full, for a barrier or a device-wide synchronise between two

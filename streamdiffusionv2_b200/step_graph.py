@@ -85,6 +85,10 @@ class StepGraphs:
         self.replays = 0
         self.eager_steps = 0
 
+    def forget(self) -> None:
+        """Drop every recording (their block ranges or tensors are no longer the pipeline's)."""
+        self._graphs.clear()
+
     # ------------------------------------------------------------------ host side of a step
     @staticmethod
     def steady(layers: Sequence[tuple], starts: Sequence[int], n_new: int) -> bool:

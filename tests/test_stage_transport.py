@@ -126,6 +126,46 @@ def _worker_restart(rank, world, port, ranges, q):
             dist.destroy_process_group()
 
 
+def _worker_rebalance(rank, world, port, ranges_a, ranges_b, q):
+    """4 chunks on one block split, the ring emptied, blocks (with their K/V state) moved, 4 more chunks."""
+    try:
+        _init(rank, world, port)
+        import fake_ops
+        from model_harness import build_pipeline
+        from streamdiffusionv2_b200.pipeline_runner import PipelineStageRunner
+        from streamdiffusionv2_b200.stage_transport import StageLink
+        fake_ops.install(_Patch())
+        case = cases.MODEL_CASES["m_stages"]
+        fs, sched = cases.model_schedule(case)
+        pipe, first, chunks = build_pipeline(case)
+        role = "input" if rank == 0 else ("output" if rank == world - 1 else "middle")
+        outs = []
+        with torch.no_grad():
+            torch.manual_seed(case["seed"] + 1)
+            pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
+                         current_start=0, current_end=fs * (1 + case["frames"]), block_mode=role)
+            torch.manual_seed(case["seed"] + 2)
+            link = StageLink(rank, world, torch.device("cpu"), (len(case["levels"]), fs * case["frames"],
+                             cases.MODEL_KW["dim"]), tuple(pipe.hidden_states.shape), dtype=torch.float32, timeout_s=60)
+            runner = PipelineStageRunner(pipe, link, rank, world, ranges_a)
+            for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
+                if i == 4:
+                    runner.rebalance(ranges_b)
+                o = runner.step(i, noise, cs, ce, None, last=(i == 3))
+                if o is not None:
+                    outs.append(o.clone().numpy())
+                if i == 3:
+                    runner.quiesce()
+            runner.finish()
+            owned = [i for i in range(cases.MODEL_KW["num_layers"]) if pipe.kv_cache1[i]["k"].shape[1] > 0]
+        q.put((rank, "ok", outs, (runner.block_range, owned)))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc(), None))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
 def _run(target, world, *args, timeout=240):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -203,6 +243,26 @@ def test_prompt_restart_travels_the_ring_and_the_links_stay_usable():
     assert res[0][1] == ["sent"]
     assert res[1][1] == ["prompt two \u2713"] and res[2][1] == ["prompt two \u2713"]
     assert res[2][2] == 6 and res[0][2] == 0
+
+
+@pytest.mark.parametrize("a,b", [([[0, 2], [2, 3]], [[0, 1], [1, 3]]), ([[0, 1], [1, 3]], [[0, 2], [2, 3]])])
+def test_blocks_move_between_stages_with_their_cache_state(a, b):
+    """Rebalancing mid-stream must not change the stream: the moved block's K/V, index tensors and
+    evict queue travel with it, so the outputs equal the reference fixture's."""
+    case = cases.MODEL_CASES["m_stages"]
+    _, z = cases.load_fixture("m_stages")
+    res = _run(_worker_rebalance, 2, a, b)
+    for r, v in res.items():
+        assert v[0] == "ok", v[1]
+    outs = res[1][1]
+    assert len(outs) == case["chunks"]
+    for i, o in enumerate(outs):
+        assert np.abs(o - z[f"out_{i}"]).max() < 5e-4, i
+    assert res[0][2][0] == b[0] and res[1][2][0] == b[1]
+    moved = (set(range(*a[0])) ^ set(range(*b[0])))
+    for r in (0, 1):     # the giver holds a placeholder for what it gave away
+        gave = moved & set(range(*a[r]))
+        assert not (gave & set(res[r][2][1]))
 
 
 def test_three_rank_pipeline_runs_with_a_middle_stage():
