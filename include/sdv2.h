@@ -127,6 +127,9 @@ int sdv2_rope_kv_append_indirect(const sdv2_view* q, const sdv2_view* k, const s
  * workspace_dev: at least sdv2_attn_workspace_bytes() bytes, 256-byte aligned; its first word is
  * a status flag written only when a bounded device-side wait runs out (read with sdv2_read_status;
  * zero it once after allocation).
+ * Cache rows at and beyond seq_lens[b] are never attended and may hold anything (uninitialised
+ * memory, NaN): their scores are masked and their V rows are cleared on chip before use, like
+ * flash_attn_with_kvcache's handling of rows past cache_seqlens.
  */
 int sdv2_attn_kvcache(const sdv2_view* q, const sdv2_view* k_cache, const sdv2_view* v_cache,
                       const sdv2_view* out, int rows, int q_tokens, int heads, int head_dim,
@@ -134,6 +137,12 @@ int sdv2_attn_kvcache(const sdv2_view* q, const sdv2_view* k_cache, const sdv2_v
                       void* workspace_dev, size_t workspace_bytes, void* stream);
 
 size_t sdv2_attn_workspace_bytes(int rows, int q_tokens, int heads, int head_dim);
+
+/* Partial-result slots (133,120 bytes each, after the 256-byte status block) that the attention
+ * launch for this problem writes on a device with `sm_count` multiprocessors: 0 when the grid
+ * fills whole waves or the key range is short, never more than 192.  min_seq_len = the smallest
+ * seq_lens[b].  Pure host arithmetic (no CUDA call); no reference counterpart. */
+int sdv2_attn_partial_slots(int rows, int q_tokens, int heads, int min_seq_len, int sm_count);
 
 /*
  * Text cross-attention core: every query attends all kv_tokens context slots, no mask.
@@ -166,13 +175,14 @@ int sdv2_attn_kvcache_simt(const sdv2_view* q, const sdv2_view* k_cache, const s
  * live in a device array built into the library (24.4 MiB per GPU, 192 partial slots).
  *
  *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
- *  - The first call on each device resolves the array's address and zeroes its status block; that
- *    call synchronises, so make it before any stream capture starts.
- *  - A problem whose tail split needs more than 192 partial slots is refused with
- *    SDV2_ERR_WORKSPACE before anything is launched; rows > SDV2_MAX_ROWS with
- *    SDV2_ERR_UNSUPPORTED_SHAPE.
+ *  - The first call on each device looks up the array's device address (a host-side query: nothing
+ *    is launched or synchronised).  Make that first call before any stream capture starts.
+ *  - The array always suffices: the kernel's tail split is lowered until it fits 192 partial slots
+ *    (see sdv2_attn_partial_slots), so no shape is refused for lack of scratch; SDV2_ERR_WORKSPACE is
+ *    kept as a defensive check only.  rows > SDV2_MAX_ROWS is refused with SDV2_ERR_UNSUPPORTED_SHAPE.
  *  - All calls on a device share the array and it keeps the previous call's contents (every slot is
- *    rewritten before it is read).  Calls that overlap on the GPU race on it: order them.
+ *    rewritten before it is read; the status block starts as zeros and is cleared by
+ *    sdv2_read_status).  Calls that overlap on the GPU race on it: order them.
  *  - status_dev_out (optional) receives the device address of the status block, valid for
  *    sdv2_read_status.
  * Results are identical to sdv2_attn_kvcache on the same inputs.
@@ -220,6 +230,18 @@ int sdv2_read_status(void* workspace_dev, int* detail, void* stream);
  */
 int sdv2_selftest_umma(const void* a_dev, const void* b_dev, const void* p_dev, const void* v_dev,
                        float* s_out_dev, float* o_out_dev, int* status_dev, void* stream);
+
+/*
+ * Device self-test of the bounded waits: one thread block waits on an on-chip barrier that nothing
+ * ever completes, gives up after `budget_cycles` SM clock cycles (clamped to [1e4, 2e9]), records
+ * the site in *status_dev and returns normally - the context stays usable.  A following
+ * sdv2_read_status(status_dev, ...) must answer SDV2_ERR_TIMEOUT with site 7 (probe) in the low
+ * byte of *detail.  This is how the error path of every wait in the attention and append kernels
+ * (same wait routine, budget 1.5e9 cycles) is exercised without hanging or faulting a GPU.
+ * No reference counterpart (the reference's communication_timeout,
+ * streamv2v/communication/data_containers.py:77, is never read).
+ */
+int sdv2_selftest_wait_timeout(int* status_dev, long long budget_cycles, void* stream);
 
 #ifdef __cplusplus
 }

@@ -64,6 +64,8 @@ _SIGNATURES = {
                                                         C.c_void_p]),
     "sdv2_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.c_void_p]),
     "sdv2_selftest_umma": (C.c_int, [C.c_void_p] * 4 + [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "sdv2_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_longlong, C.c_void_p]),
+    "sdv2_attn_partial_slots": (C.c_int, [C.c_int] * 5),
 }
 
 

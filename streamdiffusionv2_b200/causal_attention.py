@@ -26,6 +26,8 @@ from .ring_state import RingState
 
 _start_cache = {}
 _step_recorder = None
+_POLL_EVERY = 32          # attention calls between two looks at the device status word
+_calls_since_poll = 0
 
 
 def set_step_recorder(recorder) -> None:
@@ -141,8 +143,16 @@ def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_
         state._sig = RingState._signature(kv_cache)
 
     if q.dtype == torch.bfloat16:
-        return ops.attn_kvcache(roped_q, kv_cache["k"], kv_cache["v"], seq_lens)
-    return ops.attn_kvcache_simt(roped_q, kv_cache["k"], kv_cache["v"], seq_lens)
+        out = ops.attn_kvcache(roped_q, kv_cache["k"], kv_cache["v"], seq_lens)
+    else:
+        out = ops.attn_kvcache_simt(roped_q, kv_cache["k"], kv_cache["v"], seq_lens)
+    # a kernel that gave up a bounded wait wrote nothing: surface that instead of streaming garbage
+    global _calls_since_poll
+    _calls_since_poll += 1
+    if _calls_since_poll >= _POLL_EVERY and _step_recorder is None:
+        _calls_since_poll = 0
+        ops.poll_status(q.device)
+    return out
 
 
 def _fusable(x: torch.Tensor) -> bool:
@@ -232,6 +242,28 @@ def block_forward(self, x, e, seq_lens, grid_sizes, freqs, context, context_lens
     x = x + self.cross_attn(self.norm3(x), context, context_lens, crossattn_cache=crossattn_cache)
     y = self.ffn(norm_modulate(self.norm2, x, scale_f, shift_f))
     return add_gated(x, y, gate_f)
+
+
+def watch_cache_manager(manager) -> None:
+    """Make the reference's `KVCacheManager` (streamv2v/communication/kv_cache_manager.py:48-86)
+    safe to use with the host-integer slot mirror: its `broadcast_kv_blocks` writes the index tensors
+    of the moved blocks with collectives, which do not bump the tensors' version counters, so the
+    mirror would keep the old integers (and, when the donor's rank is lower than the receiver's, no
+    `+=` follows to reveal the change).  After this call every `broadcast_kv_blocks` ends by
+    invalidating the mirrors of the blocks it moved.  Idempotent."""
+    if getattr(manager, "_sdv2_watched", False):
+        return
+    original = manager.broadcast_kv_blocks
+
+    def broadcast_kv_blocks(block_indices, donor_rank):
+        try:
+            return original(block_indices, donor_rank)
+        finally:
+            for bi in block_indices:
+                RingState.invalidate(manager.pipeline.kv_cache1[bi])
+
+    manager.broadcast_kv_blocks = broadcast_kv_blocks
+    manager._sdv2_watched = True
 
 
 def install(model, fuse_block: bool = True) -> int:

@@ -11,13 +11,42 @@
 #include "sdv2_internal.h"
 
 namespace {
-
 thread_local int g_last_cuda_error = 0;
+}
 
-int cuda_fail(cudaError_t e) {
+namespace sdv2 {
+
+int record_cuda_error(cudaError_t e) {
   g_last_cuda_error = static_cast<int>(e);
   return SDV2_ERR_CUDA;
 }
+
+cudaError_t device_info(DeviceInfo* out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int sms[kMaxDevices];  // 0 = not looked up yet
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (sms[dev] == 0) {
+    int n = 0;
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    if (n <= 0) return cudaErrorInvalidDevice;
+    sms[dev] = n;
+  }
+  out->device = dev;
+  out->sms = sms[dev];
+  return cudaSuccess;
+}
+
+}  // namespace sdv2
+
+namespace {
+
+int cuda_fail(cudaError_t e) { return sdv2::record_cuda_error(e); }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -251,6 +280,14 @@ size_t sdv2_attn_workspace_bytes(int rows, int q_tokens, int heads, int head_dim
   return kStatusBytes + sdv2::kAttnMaxPartialSlots * sdv2::kAttnPartialBytesPerSlot;
 }
 
+int sdv2_attn_partial_slots(int rows, int q_tokens, int heads, int min_seq_len, int sm_count) {
+  if (rows <= 0 || q_tokens <= 0 || heads <= 0 || min_seq_len <= 0 || sm_count <= 0) return 0;
+  int n_tail = 0;
+  const int split = sdv2::attn_tail_split(static_cast<int64_t>((q_tokens + 255) / 256) * heads * rows, sm_count,
+                                          (min_seq_len + 127) / 128, true, &n_tail);
+  return n_tail * split;
+}
+
 int sdv2_attn_kvcache(const sdv2_view* q, const sdv2_view* k_cache, const sdv2_view* v_cache,
                       const sdv2_view* out, int rows, int q_tokens, int heads, int head_dim, int64_t cache_tokens,
                       const int32_t* seq_lens, float softmax_scale, void* workspace_dev, size_t workspace_bytes,
@@ -319,6 +356,15 @@ int sdv2_selftest_umma(const void* a_dev, const void* b_dev, const void* p_dev, 
   if ((rc = make_square_map(&tv, v_dev)) != SDV2_OK) return rc;
   cudaError_t e = sdv2::launch_umma_selftest(ta, tb, tv, p_dev, s_out_dev, o_out_dev, status_dev,
                                              static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? SDV2_OK : cuda_fail(e);
+}
+
+int sdv2_selftest_wait_timeout(int* status_dev, long long budget_cycles, void* stream) {
+  if (status_dev == nullptr) return SDV2_ERR_INVALID_ARG;
+  if (reinterpret_cast<uintptr_t>(status_dev) & 3u) return SDV2_ERR_MISALIGNED;
+  if (budget_cycles < 10000LL) budget_cycles = 10000LL;
+  if (budget_cycles > 2000000000LL) budget_cycles = 2000000000LL;
+  cudaError_t e = sdv2::launch_wait_timeout_selftest(status_dev, budget_cycles, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? SDV2_OK : cuda_fail(e);
 }
 

@@ -56,7 +56,6 @@ constexpr uint32_t kIdescQK = umma_idesc_bf16(kBM, kBN, false, false);
 constexpr uint32_t kIdescPV = umma_idesc_bf16(kBM, kHD, false, true);
 
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-constexpr int kMinKvTilesForSplit = 16;
 
 // S[stage] = Q[stage] (128 x 128, K-major) * K_tile^T (128 x 128, K-major); 8 steps of K = 16.
 __device__ __forceinline__ void issue_qk(uint32_t tmem_s, uint32_t sq, uint32_t sk) {
@@ -273,6 +272,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (c * 32 + i >= valid) s[c][i] = 0xFF800000u;  // -inf
+          // The V rows behind those keys lie inside the cache, so the TMA did not zero-fill them and they
+          // may hold anything, NaN included; P is 0 there, but 0 x NaN would poison the whole output row.
+          // Query tile 0 clears them in shared memory before it reports P (tile 1's P V is issued later).
+          if (stage == 0) {
+            const int it_v = 2 * j + 1;
+            ok = mbar_wait(bar(kBarKvFull + it_v % kSlots), (it_v / kSlots) & 1, abort_flag, p.status, WAIT_KV_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (row >= valid) {
+              uint8_t* vrow = gbase + kSmemKV + (it_v % kSlots) * kTileBytes + row * 128;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                *reinterpret_cast<uint4*>(vrow + 16 * i) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(vrow + kHalfTile + 16 * i) = make_uint4(0u, 0u, 0u, 0u);
+              }
+            }
+            fence_proxy_async_smem();
+          }
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -485,6 +502,25 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   }
 }
 
+// One warp waits on a barrier that nobody completes; the wait gives up after `budget` cycles and
+// reports like every other bounded wait in this library.
+__global__ void __launch_bounds__(32, 1) wait_timeout_selftest_kernel(int* status, long long budget) {
+  __shared__ __align__(8) uint64_t never_completed;
+  __shared__ int abort_word;
+  const uint32_t bar = smem_u32(&never_completed);
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    mbar_init(bar, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  volatile int* abort_flag = &abort_word;
+  if (threadIdx.x == 0) mbar_wait(bar, 0, abort_flag, status, WAIT_PROBE, budget);
+  __syncwarp();
+  // the other lanes take the same exit the kernels' roles take: they see the raised flag at once
+  if (threadIdx.x != 0) mbar_wait(bar, 0, abort_flag, nullptr, WAIT_PROBE, budget);
+}
+
 }  // namespace attn
 
 // Merge the partial results of the split tail tiles.  Block = (tail tile, query tile, group of 32
@@ -536,39 +572,20 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const __grid_constant
 
 cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                                 const AttnParams& p_in, cudaStream_t stream) {
+  static DynamicSmemGrant smem_grant;
   AttnParams p = p_in;
-  // per device and cheap, so set on every launch rather than cached per process
-  cudaError_t e = cudaFuncSetAttribute(attn::attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(attn::kSmemBytes));
-  if (e != cudaSuccess) return e;
-  int dev = 0, sms = 0;
-  e = cudaGetDevice(&dev);
-  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  DeviceInfo di;
+  cudaError_t e = device_info(&di);
+  if (e == cudaSuccess) e = smem_grant.ensure(attn::attn_fwd_kernel, static_cast<int>(attn::kSmemBytes), di.device);
   if (e != cudaSuccess) return e;
   p.pair_tiles = (p.q_tokens + 2 * attn::kBM - 1) / (2 * attn::kBM);
   const int64_t n_tiles = static_cast<int64_t>(p.pair_tiles) * p.heads * p.rows;
   if (n_tiles > 0x7FFFFFFFLL) return cudaErrorInvalidValue;
-  // One CTA per SM: with n_tiles = w * sms + tail the last wave keeps only `tail` SMs busy.  Cut each of
-  // its tiles into `split` key ranges so that the last wave takes 1/split of a tile time.
   int min_kv = 0x7FFFFFFF;
   for (int b = 0; b < p.rows; ++b) min_kv = min(min_kv, (p.seq_lens[b] + attn::kBN - 1) / attn::kBN);
-  p.n_full = static_cast<int>(n_tiles);
-  p.n_tail = 0;
-  p.split = 1;
-  const int tail = static_cast<int>(n_tiles % sms);
-  // (worth a second launch only when a tile is long: short key ranges, e.g. the 4 tiles of the text
-  // context, are dominated by per-CTA set-up)
-  if (p.part_o != nullptr && tail > 0 && min_kv >= attn::kMinKvTilesForSplit) {
-    int split = sms / tail;
-    if (split > min_kv) split = min_kv;
-    if (split > 32) split = 32;
-    while (split >= 2 && tail * split > kAttnMaxPartialSlots) --split;
-    if (split >= 2) {
-      p.n_tail = tail;
-      p.n_full = static_cast<int>(n_tiles) - tail;
-      p.split = split;
-    }
-  }
+  // whole tiles keep the head-major order; the tiles of the last, partly filled wave are cut into key ranges
+  p.split = attn_tail_split(n_tiles, di.sms, min_kv, p.part_o != nullptr, &p.n_tail);
+  p.n_full = static_cast<int>(n_tiles) - p.n_tail;
   const unsigned grid = static_cast<unsigned>(p.n_full + p.n_tail * p.split);
   attn::attn_fwd_kernel<<<grid, attn::kThreads, attn::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
   e = cudaGetLastError();
@@ -580,13 +597,20 @@ cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k
 cudaError_t launch_umma_selftest(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_v,
                                  const void* p_dev, float* s_out, float* o_out, int* status,
                                  cudaStream_t stream) {
+  static DynamicSmemGrant smem_grant;
   const int smem = 3 * attn::kTileBytes + 128 + 1024;
-  cudaError_t attr =
-      cudaFuncSetAttribute(attn::umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  DeviceInfo di;
+  cudaError_t attr = device_info(&di);
+  if (attr == cudaSuccess) attr = smem_grant.ensure(attn::umma_selftest_kernel, smem, di.device);
   if (attr != cudaSuccess) return attr;
   attn::umma_selftest_kernel<<<1, 128, smem, stream>>>(tm_a, tm_b, tm_v,
                                                       static_cast<const __nv_bfloat16*>(p_dev), s_out, o_out,
                                                       status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_timeout_selftest(int* status, long long budget_cycles, cudaStream_t stream) {
+  attn::wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(status, budget_cycles);
   return cudaGetLastError();
 }
 

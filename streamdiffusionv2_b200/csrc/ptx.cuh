@@ -60,7 +60,7 @@ enum WaitSite : int {
 constexpr long long kWaitBudgetCycles = 1500000000LL;  // well under a second of SM clock
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int site) {
+                                          int* status, int site, long long budget = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
@@ -68,7 +68,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (int i = 0; i < 32; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > budget) {
       *abort_flag = 1;
       if (status) atomicCAS(status, 0, site | (static_cast<int>(blockIdx.x & 0xFFFF) << 8));
       return false;

@@ -334,9 +334,10 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
 static uint32_t magic_of(uint32_t d) { return static_cast<uint32_t>(((1ull << 32) + d - 1) / d); }
 
 template <typename T>
-static cudaError_t launch_staged(const AppendParams& p, int grid, int threads, uint32_t smem, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(rope_kv_append_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
+static cudaError_t launch_staged(const AppendParams& p, int device, int grid, int threads, uint32_t smem,
+                                 cudaStream_t stream) {
+  static DynamicSmemGrant smem_grant;  // one per instantiation
+  cudaError_t e = smem_grant.ensure(rope_kv_append_staged_kernel<T>, static_cast<int>(smem), device);
   if (e != cudaSuccess) return e;
   rope_kv_append_staged_kernel<T><<<grid, threads, smem, stream>>>(p);
   return cudaGetLastError();
@@ -387,15 +388,14 @@ cudaError_t launch_rope_kv_append(const AppendParams& p_in, int dtype, cudaStrea
     p.stage_bytes = (3u * best_tt * row_bytes + best_tt * mult_row + 127u) & ~127u;
     p.stages = staged::kStagesWanted;
     const uint32_t smem = p.stages * p.stage_bytes + staged::kTailBytes;
-    int dev = 0, sms = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    DeviceInfo di;
+    cudaError_t e = device_info(&di);
     if (e != cudaSuccess) return e;
     const int64_t total = static_cast<int64_t>(p.rows) * p.tokens;
-    const int grid = static_cast<int>(total < sms ? total : sms);
+    const int grid = static_cast<int>(total < di.sms ? total : di.sms);
     const int threads = (best_w + staged::kProducerWarps) * 32;
-    return dtype == SDV2_DTYPE_BF16 ? launch_staged<__nv_bfloat16>(p, grid, threads, smem, stream)
-                                    : launch_staged<float>(p, grid, threads, smem, stream);
+    return dtype == SDV2_DTYPE_BF16 ? launch_staged<__nv_bfloat16>(p, di.device, grid, threads, smem, stream)
+                                    : launch_staged<float>(p, di.device, grid, threads, smem, stream);
   }
   const int tok_per_block = 256 / vph;
   dim3 grid((p.tokens + tok_per_block - 1) / tok_per_block, p.heads, p.rows);

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/sdv2.h"
 
 namespace sdv2 {
@@ -55,6 +57,58 @@ struct AttnParams {
 constexpr int kAttnMaxPartialSlots = 192;
 constexpr size_t kAttnStatusBytes = 256;
 constexpr size_t kAttnPartialBytesPerSlot = 2 * 128 * 128 * 4 + 2 * 2 * 128 * 4;
+constexpr int kAttnMinKvTilesForSplit = 16;
+
+// Tail split of the attention grid.  With one CTA per SM, n_tiles = w * sms + tail leaves only
+// `tail` SMs busy in the last wave; each of those tiles is cut into `split` key ranges so that the
+// last wave takes 1/split of a tile time.  Worth a second launch only when a tile is long
+// (min_kv_tiles >= kAttnMinKvTilesForSplit).  The split is lowered until tail * split partial
+// slots fit in kAttnMaxPartialSlots, so scratch of that many slots always suffices.
+// Returns the split (1 = no split); *n_tail = tiles that are split.
+inline int attn_tail_split(int64_t n_tiles, int sms, int min_kv_tiles, bool have_scratch, int* n_tail) {
+  *n_tail = 0;
+  if (sms <= 0 || !have_scratch) return 1;
+  const int tail = static_cast<int>(n_tiles % sms);
+  if (tail == 0 || min_kv_tiles < kAttnMinKvTilesForSplit) return 1;
+  int split = sms / tail;
+  if (split > min_kv_tiles) split = min_kv_tiles;
+  if (split > 32) split = 32;
+  while (split >= 2 && tail * split > kAttnMaxPartialSlots) --split;
+  if (split < 2) return 1;
+  *n_tail = tail;
+  return split;
+}
+
+// Per-device facts that never change while the process lives, looked up once per device.
+struct DeviceInfo {
+  int device;
+  int sms;
+};
+cudaError_t device_info(DeviceInfo* out);
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device, per-function setting: one instance
+// of this class per kernel remembers what was already granted on each device, so that a launch
+// makes the runtime call only the first time (or when it needs more than before).
+class DynamicSmemGrant {
+ public:
+  template <typename Kernel>
+  cudaError_t ensure(Kernel kernel, int bytes, int device) {
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu_);
+    if (granted_[device] >= bytes) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) granted_[device] = bytes;
+    return e;
+  }
+
+ private:
+  static constexpr int kMaxDevices = 64;
+  std::mutex mu_;
+  int granted_[kMaxDevices] = {};
+};
+
+// Records a failing CUDA call for sdv2_last_cuda_error() and returns SDV2_ERR_CUDA.
+int record_cuda_error(cudaError_t e);
 
 cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                                 const AttnParams& p, cudaStream_t stream);
@@ -70,5 +124,7 @@ cudaError_t launch_attn_simt(const SimtAttnParams& p, int dtype, cudaStream_t st
 cudaError_t launch_umma_selftest(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_v,
                                  const void* p_dev, float* s_out, float* o_out, int* status,
                                  cudaStream_t stream);
+
+cudaError_t launch_wait_timeout_selftest(int* status, long long budget_cycles, cudaStream_t stream);
 
 }  // namespace sdv2

@@ -267,6 +267,63 @@ def read_status(device: torch.device) -> None:
     N.check(rc, "sdv2_read_status")
 
 
+class _StatusPoll:
+    """Asynchronous watch on a device's status word: a 4-byte copy to pinned host memory rides the
+    launching stream, and its result is looked at by a later poll once the copy's event has
+    completed.  Never blocks the host; a raised status is seen one or two polls late."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.word = workspace(device)[:4].view(torch.int32)
+        self.pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event: Optional[torch.cuda.Event] = None
+
+    def poll(self) -> None:
+        if self.event is not None:
+            if not self.event.query():
+                return
+            self.event = None
+            seen = int(self.pinned[0])
+            if seen != 0:
+                read_status(self.device)        # synchronises, decodes, clears and raises
+                raise N.NativeError(N.ERR_TIMEOUT, "device status",
+                                    f"a kernel reported status {seen:#x} earlier; its outputs are not valid")
+        self.pinned.copy_(self.word, non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+
+_polls: Dict[int, _StatusPoll] = {}
+
+
+def poll_status(device: torch.device) -> None:
+    """Cheap, non-blocking check that no kernel of this library gave up a bounded wait or refused
+    device-resident parameters since the last check; raises NativeError if one did (its launch
+    wrote nothing, so everything computed from its outputs is garbage).  Called by the attention
+    forwards every few dozen launches and after every graph replay; not during stream capture."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        return
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    p = _polls.get(idx)
+    if p is None:
+        p = _polls[idx] = _StatusPoll(torch.device("cuda", idx))
+    p.poll()
+
+
+def selftest_wait_timeout(device: torch.device, budget_cycles: int = 2_000_000) -> None:
+    """Launch the self-test block whose wait nobody satisfies, into this device's status word.  The
+    next `read_status` / `poll_status` then reports a timeout at the probe site (7)."""
+    ws = workspace(device)
+    rc = N.lib().sdv2_selftest_wait_timeout(ws.data_ptr(), int(budget_cycles), N.stream_ptr(device))
+    N.check(rc, "sdv2_selftest_wait_timeout")
+
+
+def attn_partial_slots(rows: int, q_tokens: int, heads: int, min_seq_len: int, sm_count: int) -> int:
+    """Scratch slots the attention launch for this problem uses on a device with `sm_count` SMs."""
+    return int(N.lib().sdv2_attn_partial_slots(rows, q_tokens, heads, min_seq_len, sm_count))
+
+
 def selftest_umma(a: torch.Tensor, b: torch.Tensor, p: torch.Tensor, v: torch.Tensor):
     """(a @ b^T, p @ v) for 128x128 bf16 matrices through the two tensor-core code paths."""
     dev = a.device

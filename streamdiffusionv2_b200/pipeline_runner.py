@@ -20,6 +20,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
+from .ring_state import RingState
 from .stage_transport import StageLink, StagePacket, contiguous_block_ranges
 from .stream_pipeline import StreamPipeline, assign_ints
 
@@ -206,7 +207,7 @@ class PipelineStageRunner:
                           kv["v"].to(dev)):
                     dist.send(t.contiguous(), dst=dst)
                 kv["k"], kv["v"] = kv["k"][:, :0], kv["v"][:, :0]         # placeholder, as for never-owned blocks
-                kv.pop("_sdv2_host", None)
+                RingState.invalidate(kv)
             else:
                 rows = pipe.hidden_states.shape[0]
                 meta = torch.zeros(3 + rows * (1 + self._QUEUE_SLOTS), dtype=torch.int64, device=dev)
@@ -223,7 +224,7 @@ class PipelineStageRunner:
                 for t in (ge, le, k, v):
                     dist.recv(t, src=src)
                 kv.update(k=k, v=v, global_end_index=ge, local_end_index=le, current_step=m[1], total_steps=m[2])
-                kv.pop("_sdv2_host", None)            # the host mirror is re-read from the received tensors
+                RingState.invalidate(kv)              # the host mirror is re-read from the received tensors
                 queues = []
                 for r in range(rows):
                     base = 3 + r * (1 + self._QUEUE_SLOTS)

@@ -10,7 +10,12 @@ State ownership is unchanged: the evict queue stays on the attention module (`ev
 causal_model.py:179), `current_step` / `total_steps` stay in the cache dict
 (models/wan/causal_stream_inference.py:98-105).  The mirror lives under the private key
 `_sdv2_host` of the cache dict and is re-read from the device tensors whenever they were replaced
-or written by anyone else (detected through the tensors' identity, data pointer and version).
+or written through PyTorch ops that bump the tensors' version counter (`+=`, `fill_`, `copy_`,
+index assignment: detected through the tensors' identity, data pointer and version).  Writers that
+bypass the version counter are NOT detected: c10d collectives (`dist.broadcast` / `recv` into the
+index tensors, as streamv2v/communication/kv_cache_manager.py:72-78 does), raw CUDA copies, other
+libraries' kernels.  After such a write call `RingState.invalidate(kv_cache)`;
+`causal_attention.watch_cache_manager` does that for the reference's `KVCacheManager`.
 """
 from __future__ import annotations
 
@@ -51,6 +56,13 @@ class RingState:
             st = cls([int(x) for x in g], [int(x) for x in l], sig)
             kv_cache[_KEY] = st
         return st
+
+    @staticmethod
+    def invalidate(kv_cache: dict) -> None:
+        """Forget the host mirror of this cache dict; the next call re-reads both index tensors from
+        the device (one read-back).  Needed after anything wrote `global_end_index` /
+        `local_end_index` without bumping their version counters (a collective, a raw copy)."""
+        kv_cache.pop(_KEY, None)
 
     @staticmethod
     def _ensure_queues(kv_cache: dict, attn_module) -> None:

@@ -158,6 +158,7 @@ class StepGraphs:
             self._stage_params(rec, starts)
         rec.graph.replay()
         self.replays += 1
+        ops.poll_status(self.device)       # replays bypass the attention forwards, which poll on the eager path
         log = ops.current_launch_log()
         if log is not None:
             for name, c in rec.launch_counts.items():

@@ -18,7 +18,6 @@ import argparse
 import json
 import os
 import sys
-import types
 
 import numpy as np
 import torch
@@ -29,36 +28,10 @@ import cases  # noqa: E402
 
 
 def import_reference(root: str):
-    sys.dont_write_bytecode = True
-
-    def stub(name, **attrs):
-        m = types.ModuleType(name)
-        m.__dict__.update(attrs)
-        sys.modules[name] = m
-
-    class ConfigMixin:
-        pass
-
-    class ModelMixin(torch.nn.Module):
-        pass
-
-    stub("diffusers")
-    stub("diffusers.configuration_utils", ConfigMixin=ConfigMixin, register_to_config=lambda f: f)
-    stub("diffusers.models")
-    stub("diffusers.models.modeling_utils", ModelMixin=ModelMixin)
-    stub("diffusers.utils", export_to_video=lambda *a, **k: None)
-    stub("ftfy", fix_text=lambda s: s)
-    sys.path.insert(0, root)
-    import models.wan.causal_model as cm
-    import models.wan.wan_base.modules.attention as att
-    import models.wan.wan_base.modules.model as wm
-    import models.wan.causal_stream_inference as csi
-    import models.wan.wan_wrapper as ww
-    import models.wan.flow_match as fm
-    cm.FLASH_ATTN_AVAILABLE = False
-    att.FLASH_ATTN_2_AVAILABLE = False
-    att.FLASH_ATTN_3_AVAILABLE = False
-    return types.SimpleNamespace(cm=cm, att=att, wm=wm, csi=csi, ww=ww, fm=fm)
+    """The reference's modules, forced onto its own PyTorch attention paths (oracle/reference_shim.py)."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle.reference_shim import import_reference as _imp
+    return _imp(root, flash_attn=False)
 
 
 class _Feed(torch.nn.Module):
@@ -174,7 +147,7 @@ def run_trace_case(ref, case: dict) -> dict:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("SDV2_REFERENCE"), required="SDV2_REFERENCE" not in os.environ)
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     ref = import_reference(args.reference)

@@ -3,7 +3,6 @@ tiny seeded model (CPU, fp32).  Called from make_golden.py."""
 from __future__ import annotations
 
 import os
-import types
 
 import numpy as np
 import torch
@@ -11,41 +10,13 @@ import torch
 import cases
 
 
-def build_reference_pipeline(ref, case, block_mode="input"):
-    model = ref.cm.CausalWanModel(**cases.MODEL_KW)
-    cases.seed_parameters(model)
-    model.eval()
-    wrapper = ref.ww.CausalWanDiffusionWrapper.__new__(ref.ww.CausalWanDiffusionWrapper)
-    torch.nn.Module.__init__(wrapper)
-    wrapper.model = model
-    wrapper.uniform_timestep = False
-    wrapper.scheduler = ref.fm.FlowMatchScheduler(shift=8.0, sigma_min=0.0, extra_one_step=True)
-    wrapper.scheduler.set_timesteps(1000, training=True)
-    wrapper.seq_len = 32760
-    wrapper.post_init()
-
+def build_reference_pipeline(ref, case, block_mode="input", device="cpu", dtype=torch.float32):
+    """The reference's own pipeline objects for a model case (oracle/reference_shim.py)."""
+    from oracle.reference_shim import build_reference_pipeline as _build
     prompt, first, chunks = cases.model_inputs(case)
-    pipe = ref.csi.CausalStreamInferencePipeline.__new__(ref.csi.CausalStreamInferencePipeline)
-    torch.nn.Module.__init__(pipe)
-    pipe.device = torch.device("cpu")
-    pipe.generator = wrapper
-    pipe.text_encoder = lambda text_prompts: {"prompt_embeds": prompt.clone()}
-    pipe.scheduler = wrapper.get_scheduler()
-    pipe.denoising_step_list = torch.tensor(case["levels"], dtype=torch.long)
-    pipe.num_transformer_blocks = cases.MODEL_KW["num_layers"]
-    pipe.num_heads = cases.MODEL_KW["num_heads"]
     h, w = case["latent_hw"]
-    pipe.frame_seq_length = (h // 2) * (w // 2)
-    pipe.num_kv_cache = case["cache_frames"]
-    pipe.kv_cache_length = pipe.frame_seq_length * pipe.num_kv_cache
-    pipe.num_sink_tokens = case["sink"]
-    pipe.adapt_sink_threshold = -1
-    pipe.num_frame_per_block = case["frames"]
-    model.num_frame_per_block = case["frames"]
-    pipe.conditional_dict = None
-    pipe.kv_cache1 = pipe.kv_cache2 = pipe.hidden_states = pipe.block_x = None
-    pipe.args = types.SimpleNamespace()
-    return pipe
+    return _build(ref, cases.MODEL_KW, case["levels"], (h // 2) * (w // 2), case["cache_frames"], case["sink"],
+                  case["frames"], prompt, device=device, dtype=dtype, init_parameters=cases.seed_parameters)
 
 
 def snapshot(pipe, layer):

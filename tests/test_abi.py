@@ -56,3 +56,24 @@ def test_no_fallback_when_library_missing(monkeypatch, tmp_path):
     monkeypatch.setattr(_native, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no fallback"):
         _native.lib()
+
+
+def test_tail_split_never_needs_more_than_the_fixed_scratch(built_lib):
+    """The attention launcher and the allocation-free entry point share one split routine; for any
+    SM count and problem it asks for at most 192 partial slots (what both scratch areas hold)."""
+    from streamdiffusionv2_b200 import _native as N
+    slots = N.lib().sdv2_attn_partial_slots
+    # the production shape on a 148-SM part: 13 tile pairs x 12 heads x 2 rows = 312 = 2 x 148 + 16;
+    # 148 // 16 = 9 key ranges per tail tile
+    assert slots(2, 3120, 12, 32760, 148) == 16 * 9
+    assert slots(2, 3120, 12, 15 * 128, 148) == 0          # key range too short to be worth a second launch
+    assert slots(1, 256, 148, 32760, 148) == 0             # whole waves
+    worst = 0
+    for sms in (1, 7, 64, 108, 132, 148, 160, 192, 193, 256, 1024):
+        for rows, q, heads in ((1, 256, 1), (2, 3120, 12), (4, 3120, 40), (16, 1560, 40), (64, 4680, 12), (3, 300, 5)):
+            for seq in (128, 2047, 2048, 32760, 49920):
+                n = slots(rows, q, heads, seq, sms)
+                assert 0 <= n <= 192, (sms, rows, q, heads, seq, n)
+                worst = max(worst, n)
+    assert worst > 100      # the bound is actually approached, so the clamp matters
+    assert slots(0, 1, 1, 1, 1) == 0 and slots(1, 1, 1, 1, 0) == 0

@@ -14,9 +14,11 @@ import torch
 import cases
 import fake_ops
 
-REFERENCE = os.environ.get("SDV2_REFERENCE", "/root/reference")
-pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "models", "wan")),
-                                reason="reference checkout not present")
+from oracle.reference_shim import reference_root
+
+# $SDV2_REFERENCE (a checkout) or baseline/_ref (the reference pip-installed with --target)
+REFERENCE = reference_root()
+pytestmark = pytest.mark.skipif(REFERENCE is None, reason="reference not present (checkout or baseline/_ref)")
 
 
 @pytest.fixture(scope="module")

@@ -115,3 +115,35 @@ def test_external_index_writes_are_picked_up(monkeypatch):
     st2 = RingState.of(kv)
     assert st2.global_end == [18, 18] and st2.local_end == [18, 18]
     assert RingState.of(kv) is st2       # no re-read while nothing changed
+
+
+def test_device_status_surfaces_from_the_streaming_entry_points(monkeypatch):
+    """A kernel that gave up a bounded wait (or refused its parameters) writes nothing; the forwards
+    look at the device status word every few attention calls so that the stream stops with an error
+    instead of carrying garbage.  Here the look itself is replaced by a host-side fake."""
+    fake_ops.install(monkeypatch)
+    from streamdiffusionv2_b200 import _native, causal_attention, ops
+    case = cases.MODEL_CASES["m_stream"]
+    pipe, first, chunks = build_pipeline(case)
+    fs, sched = cases.model_schedule(case)
+    state = {"raised": False, "polls": 0}
+
+    def poll(device):
+        state["polls"] += 1
+        if state["raised"]:
+            raise _native.NativeError(_native.ERR_TIMEOUT, "device status", "a kernel reported status 0x7 earlier")
+
+    monkeypatch.setattr(ops, "poll_status", poll)
+    monkeypatch.setattr(causal_attention, "_POLL_EVERY", 2)
+    with torch.no_grad():
+        pipe.prepare(text_prompts=["p"], device=torch.device("cpu"), dtype=torch.float32, noise=first,
+                     current_start=0, current_end=fs * (1 + case["frames"]))
+        pipe.inference_stream(noise=chunks[0], current_start=sched[0][0], current_end=sched[0][1])
+        assert state["polls"] >= 1               # the healthy path polls and goes on
+        state["raised"] = True
+        with pytest.raises(_native.NativeError, match="status"):
+            pipe.inference_stream(noise=chunks[1], current_start=sched[1][0], current_end=sched[1][1])
+        # the entry point the pipeline-stage runner calls
+        with pytest.raises(_native.NativeError, match="status"):
+            pipe.inference(noise=chunks[2], current_start=sched[2][0], current_end=sched[2][1], current_step=None,
+                           block_mode="input", block_num=[0, 2])

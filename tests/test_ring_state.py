@@ -94,3 +94,96 @@ def test_step_graph_steady_state_predicate_matches_the_slot_logic():
     assert seen_steady >= 8
     mod.adapt_sink_thr = 0.5                      # the adaptive sink test reads the device: never recorded
     assert not StepGraphs.steady([(mod, kv)], history, n_new)
+
+
+# ---------------------------------------------------------------------------------------------
+# writers that bypass the version counter (collectives)
+# ---------------------------------------------------------------------------------------------
+import os  # noqa: E402
+import socket  # noqa: E402
+import traceback  # noqa: E402
+
+import torch.distributed as dist  # noqa: E402
+import torch.multiprocessing as mp  # noqa: E402
+
+
+class _FakePipeline:
+    def __init__(self, kv):
+        self.kv_cache1 = [kv]
+
+
+class _ManagerLike:
+    """The part of the reference's KVCacheManager that matters here
+    (streamv2v/communication/kv_cache_manager.py:48-86): broadcast the index tensors in place."""
+
+    def __init__(self, kv):
+        self.pipeline = _FakePipeline(kv)
+
+    def broadcast_kv_blocks(self, block_indices, donor_rank):
+        for bi in block_indices:
+            dist.broadcast(self.pipeline.kv_cache1[bi]["global_end_index"], src=donor_rank)
+            dist.broadcast(self.pipeline.kv_cache1[bi]["local_end_index"], src=donor_rank)
+
+
+def _broadcast_worker(rank, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        torch.set_num_threads(1)
+        dist.init_process_group("gloo", rank=rank, world_size=2)
+        from streamdiffusionv2_b200.causal_attention import watch_cache_manager
+        fs, smax, n_new = 6, 42, 12
+        kv = {"k": torch.empty(1, smax, 1, 0), "v": torch.empty(1, smax, 1, 0),
+              "global_end_index": torch.tensor([0]), "local_end_index": torch.tensor([0]),
+              "total_steps": 1, "current_step": 1}
+        mod = _Mod(1)
+        steps = 2 if rank == 0 else 1          # the donor (rank 0) is one chunk ahead
+        for s in range(steps):
+            st = RingState.of(kv)
+            st.plan(kv, mod, [s * n_new], n_new, fs)
+            kv["global_end_index"].data[:] = torch.tensor(st.global_end)
+            kv["local_end_index"].data[:] = torch.tensor(st.local_end)
+        version = kv["global_end_index"]._version
+        mgr = _ManagerLike(kv)
+        plain_stale = None
+        if rank == 1:
+            # without the hook: the collective changes the values, not the version, and the mirror stays stale
+            mgr.broadcast_kv_blocks([0], 0)
+            assert kv["global_end_index"].tolist() == [24] and kv["global_end_index"]._version == version
+            plain_stale = RingState.of(kv).global_end == [12]
+            kv["global_end_index"].data[:] = torch.tensor([12])      # put the old values back for the second round
+            kv["local_end_index"].data[:] = torch.tensor([12])
+        else:
+            mgr.broadcast_kv_blocks([0], 0)
+        watch_cache_manager(mgr)
+        watch_cache_manager(mgr)               # idempotent
+        mgr.broadcast_kv_blocks([0], 0)
+        st = RingState.of(kv)
+        dst, lens = st.plan(kv, mod, [24], n_new, fs)
+        q.put((rank, "ok", (plain_stale, st.global_end, dst, lens)))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def test_collective_writes_to_index_tensors_need_and_get_invalidation():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_broadcast_worker, args=(r, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in procs:
+        r = q.get(timeout=120)
+        res[r[0]] = r
+    for p in procs:
+        p.join(30)
+    for r in (0, 1):
+        assert res[r][1] == "ok", res[r][2]
+    plain_stale, ge, dst, lens = res[1][2]
+    assert plain_stale is True                 # the failure mode exists: version counters do not see collectives
+    # after the hooked broadcast the receiver plans its next chunk from the donor's values
+    assert ge == [36] and dst == [24] and lens == [36]
+    assert res[0][2][1:] == ([36], [24], [36])
