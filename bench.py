@@ -98,65 +98,155 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU arm: the oracle's restatement of the reference attention path on the host cores
+# CPU arm: the reference's attention path on the host cores
 # ---------------------------------------------------------------------------------------------
 
-def cpu_attention_path(samples: int, warmup: int, q_tokens: int, budget_s: float = 150.0):
-    """Times rope + slot write + attention over the full 21-frame cache for one layer and the 2
-    cache rows of the workload (bf16 tensors, fp32 math on CPU, as the reference does there), on
-    `q_tokens` of the chunk's 3120 query tokens per row.  Returns seconds per full layer call
-    (scaled to 3120 query tokens) per sample."""
+def _cpu_layer(H, rows, dtype, total_steps):
+    """(call, kind): one full-size call of the cached self-attention path on CPU tensors - rope,
+    ring slot write, index update, attention over the whole cache.  The reference's own
+    CausalWanSelfAttention module when the reference is installed beside the benchmark
+    (baseline/_ref), else the oracle's restatement of it."""
     from oracle import causal_attention_oracle as orc
-    torch.set_num_threads(os.cpu_count() or 1)
-    H, D, B = MODEL_1P3B["num_heads"], 128, len(LEVELS)
-    smax = CACHE_FRAMES * FRAME_TOKENS
-    n_full = FRAMES_PER_CHUNK * FRAME_TOKENS
-    g = torch.Generator().manual_seed(0)
+    from oracle.reference_shim import import_reference, reference_root
+    D, smax = 128, CACHE_FRAMES * FRAME_TOKENS
+    root = reference_root()
+    if root is not None:
+        ref = import_reference(root, flash_attn=False)      # flash-attn has no CPU kernels
+        layer = ref.cm.CausalWanSelfAttention(dim=H * D, num_heads=H, qk_norm=False)
+
+        class Feed(torch.nn.Module):                        # q/k/v arrive projected: the path starts after the GEMMs
+            value = None
+
+            def forward(self, x):
+                return self.value
+
+        layer.q, layer.k, layer.v, layer.o = Feed(), Feed(), Feed(), torch.nn.Identity()
+        layer.sink_size, layer.adapt_sink_thr = 1, -1
+        table = orc.rope_table(D)
+        kv = {"k": torch.zeros(rows, smax, H, D, dtype=dtype), "v": torch.zeros(rows, smax, H, D, dtype=dtype),
+              "global_end_index": torch.zeros(rows, dtype=torch.long),
+              "local_end_index": torch.zeros(rows, dtype=torch.long),
+              "total_steps": total_steps, "current_step": total_steps}
+
+        def call(q, k, v, starts, frames):
+            n = frames * FRAME_TOKENS
+            layer.q.value, layer.k.value, layer.v.value = (t.flatten(2) for t in (q, k, v))
+            grid = torch.tensor([[frames, 30, 52]] * len(starts), dtype=torch.long)
+            cs = torch.tensor(starts, dtype=torch.long)
+            with torch.no_grad():
+                return layer(torch.zeros(len(starts), n, 1, dtype=dtype), None, grid, table, None, kv, cs, cs + n)
+
+        return call, "reference", kv, layer
+    cache = orc.OracleCache.zeros(rows, smax, H, D, dtype, total_steps=total_steps)
     table = orc.rope_table(D)
-    kc = torch.randn(B, smax, H, D, generator=g).to(torch.bfloat16)
-    vc = torch.randn(B, smax, H, D, generator=g).to(torch.bfloat16)
-    q, k, v = (torch.randn(B, n_full, H, D, generator=g).to(torch.bfloat16) for _ in range(3))
-    times = []
-    t_begin = time.time()
-    for i in range(warmup + samples):
+
+    def call(q, k, v, starts, frames):
+        return orc.self_attention_step(q, k, v, cache, table, (frames, 30, 52), starts, 1)[0]
+
+    return call, "port", cache, None
+
+
+def cpu_hot_path(max_steps: int, budget_s: float, layers_per_step: int):
+    """Whole chunk steps of the attention path on the host cores at the N=1 workload's shape: per
+    step `layers_per_step` full-size layer calls (2 cache rows x 3120 new tokens x 12 heads against
+    the full 32760-token cache, bf16 tensors, fp32 math as the reference does on CPU).  Nothing is
+    sub-sampled or scaled.  Runs until `max_steps` steps are done or the budget is used (at least
+    one step).  Returns (seconds per step list, kind, warm-up layer calls)."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    H, B, n_full = MODEL_1P3B["num_heads"], len(LEVELS), FRAMES_PER_CHUNK * FRAME_TOKENS
+    call, kind, state, layer = _cpu_layer(H, B, torch.bfloat16, len(LEVELS))
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(B, n_full, H, 128, generator=g).to(torch.bfloat16) for _ in range(3))
+    # start from a full, wrapped cache (what 11 chunks of streaming leave behind): random contents,
+    # local_end = cache length, the nine ring slots queued for eviction in order
+    smax = CACHE_FRAMES * FRAME_TOKENS
+    queue = list(range(2 * n_full, smax + 1, n_full))
+    if kind == "reference":
+        state.update(k=torch.randn(B, smax, H, 128, generator=g).to(torch.bfloat16),
+                     v=torch.randn(B, smax, H, 128, generator=g).to(torch.bfloat16))
+        state["local_end_index"].fill_(smax)
+        state["global_end_index"].fill_(smax)
+        layer.evict_idx = [list(queue) for _ in range(B)]
+    else:
+        state.k.copy_(torch.randn(B, smax, H, 128, generator=g))
+        state.v.copy_(torch.randn(B, smax, H, 128, generator=g))
+        state.state.local_end = [smax] * B
+        state.state.global_end = [smax] * B
+        state.state.evict_idx = [list(queue) for _ in range(B)]
+    sched = ChunkSchedule(first_frames=CACHE_FRAMES)
+    rows = [smax] * B
+
+    def layer_calls(n):
+        nonlocal rows
+        cs, _ = sched.next()
+        rows = [cs] + rows[:-1]
+        for _ in range(n):
+            call(q, k, v, rows, FRAMES_PER_CHUNK)
+
+    warm = 1
+    layer_calls(1)
+    times, t_begin = [], time.time()
+    while len(times) < max_steps:
         t0 = time.time()
-        sf = [30, 28]
-        rq = orc.rope_apply(q, (FRAMES_PER_CHUNK, 30, 52), table, sf)
-        rk = orc.rope_apply(k, (FRAMES_PER_CHUNK, 30, 52), table, sf)
-        for b, dst in enumerate((3120, 6240)):
-            kc[b, dst:dst + n_full] = rk[b]
-            vc[b, dst:dst + n_full] = v[b]
-        t_rope = time.time() - t0
-        t1 = time.time()
-        orc.attend_cache(rq[:, :q_tokens], kc, vc, [smax] * B)
-        t_att = (time.time() - t1) * (n_full / q_tokens)
-        if i >= warmup:
-            times.append(t_rope + t_att)
-        if time.time() - t_begin > budget_s and len(times) >= 1:
+        layer_calls(layers_per_step)
+        times.append(time.time() - t0)
+        if time.time() - t_begin + times[-1] > budget_s:
             break
-    return times
+    return times, kind, warm
+
+
+def cpu_single_layer_config(budget_s: float = 60.0):
+    """The single-layer configuration on the host cores as specified: 12 heads x 128, fp32, one
+    cache row of 32760 tokens, 24 steps of 3120 tokens drawn from seed 0.  Returns the median
+    seconds per step and the median over the full-cache steps (10 and later)."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    H = 12
+    call, kind, _, _ = _cpu_layer(H, 1, torch.float32, 1)
+    g = torch.Generator().manual_seed(0)
+    times, t_begin = [], time.time()
+    for s in range(24):
+        q, k, v = (torch.randn(1, 3120, H * 128, generator=g).view(1, 3120, H, 128) for _ in range(3))
+        t0 = time.time()
+        call(q, k, v, [3120 * s], 2)
+        times.append(time.time() - t0)
+        if time.time() - t_begin > budget_s:
+            break
+    steady = times[10:]
+    return {"kind": kind, "steps_run": len(times), "median_step_s": statistics.median(times),
+            "steady_state_median_s": statistics.median(steady) if steady else None, "cores": os.cpu_count() or 1,
+            "config": "1 layer, 12 heads x 128, fp32, 1 row, 32760-token cache, 24 steps x 3120 tokens, seed 0"}
+
+
+def cpu_baseline_leg(max_steps: int, budget_s: float):
+    times, kind, warm = cpu_hot_path(max_steps, budget_s, MODEL_1P3B["num_layers"])
+    step_s = statistics.median(times)
+    return {"value": VIDEO_FRAMES_PER_CHUNK / step_s, "unit": "video frames/s", "cores": os.cpu_count() or 1,
+            "kind": kind, "steps_run": len(times), "s_per_step": step_s,
+            "sample": f"{len(times)} whole chunk step(s) of the attention path: {MODEL_1P3B['num_layers']} full-size "
+                      f"layer calls each (rope + ring slot write + attention of 2 rows x 3120 queries over the full "
+                      f"32760-token cache, full and wrapping), nothing sub-sampled or scaled; {warm} layer call of warm-up; "
+                      "GEMMs, norms and FFN are outside the path and not included"}, times
 
 
 def run_reference_arm(args):
+    """`--impl reference`: the reference's CPU implementation of the path on the host cores, all
+    threads.  One step = one whole chunk step of the attention path (see cpu_hot_path); as many of
+    the requested steps as fit in the time budget are run, and `steps` / `ms_per_step` say what
+    was run and measured."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
-    q_tokens = 780 if args.steps > 8 else 3120
-    times = cpu_attention_path(args.steps, min(args.warmup, 1), q_tokens)
-    layer_s = statistics.mean(times)
-    chunk_s = layer_s * MODEL_1P3B["num_layers"]
-    fps = VIDEO_FRAMES_PER_CHUNK / chunk_s
-    sample = (f"attention path only (rope + slot write + attention over the full 32760-token cache), 1 of 30 "
-              f"layers, 2 cache rows, {q_tokens} of 3120 query tokens per row timed and scaled; chunk time = 30 x "
-              f"layer time; linear layers, norms and FFN not included")
+    base, times = cpu_baseline_leg(max(args.steps, 1), args.cpu_budget)
+    fps = base["value"]
+    base["single_layer_config"] = cpu_single_layer_config(40.0)
     line = {"impl": "reference", "metric": metric_name(), "value": fps, "unit": "video frames/s",
-            "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": chunk_s * 1e3,
+            "n_gpus": args.gpus, "steps": len(times), "warmup": 0, "ms_per_step": base["s_per_step"] * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 storage, fp32 math",
-            "data": "synthetic", "config": workload_config(args.gpus),
-            "cpu_baseline": {"value": fps, "unit": "video frames/s", "cores": cores, "kind": "port", "sample": sample},
+            "data": "synthetic", "config": workload_config(args.gpus), "cpu_baseline": base,
             "e2e": {"value": fps, "unit": "video frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+            "gpu_launches": 0, "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "note": "warm-up is one full-size layer call, not whole steps; steps = whole steps actually run "
+                    "inside the time budget"}
     args.emit(line)
 
 
@@ -199,10 +289,11 @@ def build_pipeline(device, n_layers_override=None):
 
 
 class ChunkSchedule:
-    """Chunk starts as the reference's drivers advance them, with the refresh rule."""
+    """Chunk starts as the reference's drivers advance them, with the refresh rule
+    (streamv2v/inference.py:234-252).  The first chunk (`first_frames`) was taken by prepare()."""
 
-    def __init__(self):
-        self.start = FRAME_TOKENS * (1 + FRAMES_PER_CHUNK)
+    def __init__(self, first_frames=1 + FRAMES_PER_CHUNK):
+        self.start = FRAME_TOKENS * first_frames
         self.end = self.start + FRAMES_PER_CHUNK * FRAME_TOKENS
 
     def next(self):
@@ -215,17 +306,20 @@ class ChunkSchedule:
         return cur
 
 
-def use_library_ops():
-    """Comparison arm (`--impl library`): the same model and stream, but the three cache kernels are
-    replaced by the calls the reference makes on a GPU - the fp64 complex rope chain with slice
-    writes into the cache (models/wan/causal_model.py:94-108, 321-322), flash_attn_with_kvcache
-    (:353-358), flash_attn_func for the text cross-attention (wan/modules/attention.py) - and the
-    block's norm / modulation / gate chains run as separate PyTorch ops.  The slot bookkeeping stays
-    ours (host integers, no device read-backs), so this arm is an upper bound on what the
-    reference's own loop would reach.  Library kernels only: `gpu_launches` is reported as 0."""
-    import math
-    from flash_attn import flash_attn_func, flash_attn_with_kvcache
+def use_library_ops(attention="flash_attn"):
+    """Fallback comparison arm for boxes where the reference itself is not installed: this package's
+    model and stream with the three cache kernels replaced by the calls the reference makes on a GPU
+    - the fp64 complex rope chain with slice writes into the cache (models/wan/causal_model.py:94-108,
+    321-322), flash_attn_with_kvcache (:353-358) or PyTorch SDPA (:111-157), flash_attn_func / SDPA for
+    the text cross-attention - and the block's norm / modulation / gate chains as separate PyTorch
+    ops.  The slot bookkeeping stays ours (host integers, no device read-backs), so this arm is an
+    upper bound on the reference's own loop.  Library kernels only: `gpu_launches` is 0.
+    Returns a function that restores the package's own ops."""
+    import torch.nn.functional as F
     from streamdiffusionv2_b200 import ops, wan_model
+    saved = (ops.rope_kv_append, ops.attn_kvcache, ops.cross_attn, wan_model._fusable)
+    if attention == "flash_attn":
+        from flash_attn import flash_attn_func, flash_attn_with_kvcache
 
     def rope_kv_append(q, k, v, k_cache, v_cache, table, grid, start_frames, dst_begin, *, q_out=None,
                        index_tensors=None, index_values=None):
@@ -255,23 +349,147 @@ def use_library_ops():
 
     def attn_kvcache(q, k_cache, v_cache, seq_lens, *, out=None, softmax_scale=None):
         B, n, H, D = q.shape
-        lens = torch.tensor([int(x) for x in seq_lens[:B]], dtype=torch.int32, device=q.device)
-        with ops._Logged("attn_kvcache", 4.0 * n * D * H * float(sum(int(x) for x in seq_lens[:B]))):
-            return flash_attn_with_kvcache(q, k_cache, v_cache, cache_seqlens=lens, softmax_scale=softmax_scale)
+        lens = [int(x) for x in seq_lens[:B]]
+        with ops._Logged("attn_kvcache", 4.0 * n * D * H * float(sum(lens))):
+            if attention == "flash_attn":
+                lt = torch.tensor(lens, dtype=torch.int32, device=q.device)
+                return flash_attn_with_kvcache(q, k_cache, v_cache, cache_seqlens=lt, softmax_scale=softmax_scale)
+            if all(x == k_cache.shape[1] for x in lens):
+                return F.scaled_dot_product_attention(q.transpose(1, 2), k_cache.transpose(1, 2),
+                                                      v_cache.transpose(1, 2)).transpose(1, 2).contiguous()
+            return torch.cat([F.scaled_dot_product_attention(
+                q[b:b + 1].transpose(1, 2), k_cache[b:b + 1, :x].transpose(1, 2),
+                v_cache[b:b + 1, :x].transpose(1, 2)).transpose(1, 2) for b, x in enumerate(lens)]).contiguous()
 
     def cross_attn(q, k, v, *, out=None, softmax_scale=None):
         B = q.shape[0]
         with ops._Logged("cross_attn", 4.0 * B * q.shape[1] * q.shape[3] * q.shape[2] * k.shape[1]):
-            return flash_attn_func(q, k.expand(B, -1, -1, -1), v.expand(B, -1, -1, -1), softmax_scale=softmax_scale)
+            if attention == "flash_attn":
+                return flash_attn_func(q, k.expand(B, -1, -1, -1), v.expand(B, -1, -1, -1), softmax_scale=softmax_scale)
+            return F.scaled_dot_product_attention(q.transpose(1, 2), k.expand(B, -1, -1, -1).transpose(1, 2),
+                                                  v.expand(B, -1, -1, -1).transpose(1, 2)).transpose(1, 2).contiguous()
 
     ops.rope_kv_append, ops.attn_kvcache, ops.cross_attn = rope_kv_append, attn_kvcache, cross_attn
     wan_model._fusable = lambda x: False
 
+    def restore():
+        ops.rope_kv_append, ops.attn_kvcache, ops.cross_attn, wan_model._fusable = saved
+    return restore
+
+
+def _stream_fps(pipe, device, steps, warmup, dev_chunks, first, fill_until_wrapped):
+    """prepare + fill + warm-up + `steps` timed chunk steps of a streaming pipeline object (this
+    package's or the reference's: same method names and arguments).  Returns ms per step."""
+    sched = ChunkSchedule()
+    with torch.no_grad():
+        pipe.prepare(text_prompts=["synthetic"], device=device, dtype=torch.bfloat16, noise=first, current_start=0,
+                     current_end=FRAME_TOKENS * (1 + FRAMES_PER_CHUNK))
+        for i in range(fill_until_wrapped + warmup):
+            cs, ce = sched.next()
+            pipe.inference_stream(noise=dev_chunks[i % len(dev_chunks)], current_start=cs, current_end=ce,
+                                  current_step=None)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(steps):
+            cs, ce = sched.next()
+            pipe.inference_stream(noise=dev_chunks[i % len(dev_chunks)], current_start=cs, current_end=ce,
+                                  current_step=None)
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def reference_gpu_arms(device, steps, warmup, dev_chunks, first):
+    """The reference's GPU path on the same workload, same box, same process, a few steps each.
+    With the reference installed beside the benchmark (baseline/_ref = `pip install --no-deps
+    --target`, unmodified): its own CausalWanModel under its own CausalStreamInferencePipeline,
+    (1) stock, i.e. flash_attn_with_kvcache / flash_attention where flash-attn imports,
+    (2) with flash-attn treated as absent, i.e. its PyTorch SDPA paths
+    (models/wan/causal_model.py:111-157, 373-384), and (3) the same classes after `install()`.
+    Without it: this package's model with the reference's op chain patched in (use_library_ops)."""
+    import gc
+    from oracle.reference_shim import build_reference_pipeline, import_reference, reference_root
+    out = {"steps": steps, "warmup": warmup}
+    root = reference_root()
+    g = torch.Generator(device="cpu").manual_seed(1)
+    prompt = torch.randn(1, 512, MODEL_1P3B["text_dim"], generator=g)
+
+    def init(model):
+        torch.nn.init.normal_(model.head.head.weight, std=0.02)
+
+    def run(label, flash, patch):
+        try:
+            if root is not None:
+                ref = import_reference(root, flash_attn=flash)
+                if flash and not ref.cm.FLASH_ATTN_AVAILABLE:
+                    out[label] = {"unavailable": "flash-attn does not import on this box"}
+                    return
+                torch.manual_seed(0)
+                pipe = build_reference_pipeline(ref, MODEL_1P3B, LEVELS, FRAME_TOKENS, CACHE_FRAMES, 1,
+                                                FRAMES_PER_CHUNK, prompt, device=device, dtype=torch.bfloat16,
+                                                init_parameters=init, construct_on_device=True)
+                if patch:
+                    from streamdiffusionv2_b200.causal_attention import install
+                    install(pipe.generator.model)
+                ms = _stream_fps(pipe, device, steps, warmup, dev_chunks, first, 12)
+            else:
+                restore = use_library_ops("flash_attn" if flash else "sdpa")
+                try:
+                    ms = _stream_fps(build_pipeline(device), device, steps, warmup, dev_chunks, first, 12)
+                finally:
+                    restore()
+            out[label] = {"value": VIDEO_FRAMES_PER_CHUNK / (ms / 1e3), "unit": "video frames/s", "ms_per_step": ms}
+        except Exception as e:                       # a comparison arm must not take the benchmark down
+            out[label] = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
+        finally:
+            pipe = None
+            gc.collect()
+            torch.cuda.empty_cache()
+
+    out["source"] = ("unmodified reference installed under baseline/_ref, its own model and streaming pipeline"
+                     if root is not None else
+                     "reference not installed on this box: this package's model with the reference's GPU op chain")
+    run("stock_flash_attn", True, False)
+    run("sdpa_fallback", False, False)
+    if root is not None:
+        run("with_install", False, True)
+    arms = {k: v["value"] for k, v in out.items() if isinstance(v, dict) and "value" in v and k != "with_install"}
+    if arms:
+        out["faster"] = max(arms, key=arms.get)
+        out["faster_value"] = arms[out["faster"]]
+    return out
+
+
+class LatencyStamps:
+    """Per-chunk latency under back-to-back load, on the device's own clock: an event when a
+    chunk's input copy is enqueued, an event after the copy of a step's result to the host."""
+
+    def __init__(self):
+        self.t_in, self.t_out = [], []
+
+    def enter(self):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.t_in.append(e)
+
+    def leave(self):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.t_out.append(e)
+
+    def latencies_ms(self, lag):
+        """Chunk entering at step i is final (last denoise level, on the host) after step i + lag."""
+        return [self.t_in[i].elapsed_time(self.t_out[i + lag]) for i in range(len(self.t_in) - lag)]
+
+
+def _median(xs):
+    return statistics.median(xs) if xs else None
+
 
 def run_single_gpu(args):
     from streamdiffusionv2_b200 import ops
-    if args.impl == "library":
-        use_library_ops()
+    restore = use_library_ops() if args.impl == "library" else None
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     peaks = measured_peaks()
@@ -285,6 +503,17 @@ def run_single_gpu(args):
     dev_chunks = [c.to(device) for c in host_chunks]
     host_out = torch.empty(FRAMES_PER_CHUNK, 16, h, w, dtype=torch.bfloat16).pin_memory()
     sched = ChunkSchedule()
+    levels = len(LEVELS)
+
+    def timed(n, body):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(n):
+            body(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
 
     with torch.no_grad():
         pipe.prepare(text_prompts=["synthetic"], device=device, dtype=torch.bfloat16, noise=first, current_start=0,
@@ -296,44 +525,47 @@ def run_single_gpu(args):
             cs, ce = sched.next()
             pipe.inference_stream(dev_chunks[fill % n_host], cs, ce)
             fill += 1
-        for i in range(args.warmup):
+
+        def resident_step(i):
             cs, ce = sched.next()
             pipe.inference_stream(dev_chunks[i % n_host], cs, ce)
+
+        for i in range(args.warmup):
+            resident_step(i)
         torch.cuda.synchronize()
         ops.read_status(device)
 
-        # ---- timed region 1: inputs resident in HBM
+        # ---- timed region 1: inputs resident in HBM.  Exactly K steps per region; the region is
+        # repeated until the regions together cover about two seconds, and the median counts.
         log = ops.LaunchLog(timed=not args.graphs)
         ops.set_launch_log(log)
         sampler = ClockSampler(0)
         sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
         torch.cuda.nvtx.range_push("timed")        # lets a profiler select the launches of the timed region
-        e0.record()
-        for i in range(args.steps):
-            cs, ce = sched.next()
-            pipe.inference_stream(dev_chunks[i % n_host], cs, ce)
-        e1.record()
-        torch.cuda.synchronize()
+        regions = [timed(args.steps, resident_step)]
+        ops.set_launch_log(None)
+        repeats = max(1, min(args.max_repeats, -(-int(args.min_seconds * 1e3) // max(int(regions[0]), 1))))
+        for _ in range(repeats - 1):
+            regions.append(timed(args.steps, resident_step))
         torch.cuda.nvtx.range_pop()
         clocks = sampler.stop()
-        ops.set_launch_log(None)
-        ms = e0.elapsed_time(e1)
+        ms = statistics.median(regions)
         ops.read_status(device)
 
-        # ---- timed region 2: host buffers in, host result out, every step
-        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e2.record()
-        for i in range(args.steps):
+        # ---- timed region 2: host buffers in, host result out, every step; per-chunk latency
+        stamps = LatencyStamps()
+
+        def host_step(i):
             cs, ce = sched.next()
+            stamps.enter()
             x = host_chunks[i % n_host].to(device, non_blocking=True)
             out = pipe.inference_stream(x, cs, ce)
-            host_out.copy_(out[-1], non_blocking=True)
-        e3.record()
-        torch.cuda.synchronize()
-        ms_e2e = e2.elapsed_time(e3)
+            host_out.copy_(out[-1], non_blocking=True)      # the row that just finished its last denoise level
+            stamps.leave()
+
+        regions_e2e = [timed(args.steps, host_step) for _ in range(repeats)]
+        ms_e2e = statistics.median(regions_e2e)
+        lat = stamps.latencies_ms(levels - 1)
         ops.read_status(device)
 
         # ---- per-kernel durations: launches inside a graph cannot be bracketed by events, so the
@@ -344,15 +576,19 @@ def run_single_gpu(args):
             tlog = ops.LaunchLog(timed=True)
             ops.set_launch_log(tlog)
             for i in range(min(args.steps, 6)):
-                cs, ce = sched.next()
-                pipe.inference_stream(dev_chunks[i % n_host], cs, ce)
+                resident_step(i)
             torch.cuda.synchronize()
             ops.set_launch_log(None)
             pipe.step_graphs = graphs
 
+        ref_gpu = None
+        if args.impl == "ours" and not args.no_reference_gpu:
+            ref_gpu = reference_gpu_arms(device, args.reference_steps, 2, dev_chunks, first)
+
     launches = sum(log.counts.values())
     att = tlog.durations_ms("attn_kvcache")
     app = tlog.durations_ms("rope_kv_append")
+    crs = tlog.durations_ms("cross_attn")
     att_ms = statistics.mean(att)
     att_flops = log.work["attn_kvcache"] / log.counts["attn_kvcache"]
     app_ms = statistics.mean(app)
@@ -363,19 +599,21 @@ def run_single_gpu(args):
     peak = peaks["bf16_tflops_sustained"]
     cpu = None
     if not args.no_cpu_baseline:
-        times = cpu_attention_path(3, 1, 780, budget_s=40.0)
-        layer_s = statistics.mean(times)
-        cpu = {"value": VIDEO_FRAMES_PER_CHUNK / (layer_s * MODEL_1P3B["num_layers"]), "unit": "video frames/s",
-               "cores": os.cpu_count() or 1, "kind": "port",
-               "sample": f"attention path only, 1 of 30 layers, 2 cache rows, 780 of 3120 query tokens per row timed "
-                         f"and scaled, {len(times)} samples; chunk time = 30 x layer time; linear layers not included"}
+        cpu, _ = cpu_baseline_leg(1, 1.0)
+        cpu["single_layer_config"] = cpu_single_layer_config(30.0)
     line = {
         "metric": metric_name(), "value": fps, "unit": "video frames/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(1),
+        "repeats": repeats, "region_ms": [round(r, 3) for r in regions],
         "e2e": {"value": fps_e2e, "unit": "video frames/s", "ms_per_step": ms_e2e / args.steps,
-                "h2d_bytes_per_step": host_chunks[0].numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},
+                "h2d_bytes_per_step": host_chunks[0].numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2,
+                "region_ms": [round(r, 3) for r in regions_e2e]},
+        "latency_ms": {"median": _median(lat), "max": max(lat) if lat else None, "chunks": len(lat),
+                       "definition": "per chunk under back-to-back load, device clock: from the enqueue of the "
+                                     "chunk's host->device copy to the completion of the device->host copy of its "
+                                     f"last denoise level ({levels} levels = {levels} chunk steps in the stream batch)"},
         "gpu_launches": launches, "gpu_launches_by_kernel": log.counts,
         "roofline": {"kernel": "attn_kvcache (tcgen05)", "bound": "tensor", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
@@ -383,7 +621,7 @@ def run_single_gpu(args):
                      "traffic_note": "DRAM bytes read + written per launch, one ncu capture of this shape "
                                      "(2 rows x 12 heads x 3120 queries x 32760 keys); algorithmic K+V+Q+out = 441 MB",
                      "avg_launch_ms": att_ms, "flops_per_launch": att_flops,
-                     "share_of_step": att_ms * log.counts["attn_kvcache"] / ms,
+                     "share_of_step": att_ms * log.counts["attn_kvcache"] / regions[0],
                      "timed_in": "launch-by-launch pass of the same steps after the timed region (graph replay "
                                  "hides single launches from events)" if args.graphs else "the timed region"},
         "roofline_append": {"kernel": "rope_kv_append", "bound": "hbm", "achieved": app_bytes / (app_ms * 1e-3) / 1e9,
@@ -394,11 +632,21 @@ def run_single_gpu(args):
                             "traffic_note": "DRAM bytes per launch, one ncu capture of this shape from a flushed "
                                             "cache: all 57.5 MB of reads, 11.5 MB of the 57.5 MB of writes (the "
                                             "rest is still in L2 when the kernel ends)"},
+        "cross_attn": {"avg_launch_ms": statistics.mean(crs) if crs else None,
+                       "tflops": (tlog.work["cross_attn"] / tlog.counts["cross_attn"]) / (statistics.mean(crs) * 1e-3) / 1e12
+                       if crs else None},
         "cpu_baseline": cpu, "clocks": clocks,
         "step_graphs": None if pipe.step_graphs is None else {"replayed_steps": pipe.step_graphs.replays,
                                                               "eager_steps": pipe.step_graphs.eager_steps},
     }
+    if ref_gpu is not None:
+        line["reference_gpu"] = ref_gpu
+        if ref_gpu.get("faster_value"):
+            line["speedup_vs_reference_gpu"] = fps / ref_gpu["faster_value"]
+            if isinstance(ref_gpu.get("with_install"), dict) and "value" in ref_gpu["with_install"]:
+                line["dropin_speedup_vs_reference_gpu"] = ref_gpu["with_install"]["value"] / ref_gpu["faster_value"]
     if args.impl == "library":
+        restore()
         line.update(impl="library", gpu_launches=0, gpu_launches_by_kernel={})
         line["roofline"]["kernel"] = "flash_attn_with_kvcache (library)"
         line["roofline_append"]["kernel"] = "fp64 complex rope chain + slice writes (PyTorch ops)"
@@ -476,33 +724,81 @@ def run_pipeline(args):
         barrier()
         ops.read_status(device)
 
+        def region(src, sink=None):
+            """Exactly K chunk steps on every rank between two barriers; device time of this rank."""
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record()
+            phase(args.steps, src, sink)                  # K steps on every rank; K chunks enter, K leave
+            e1.record()
+            barrier()
+            return e0.elapsed_time(e1)
+
+        def max_over_ranks(values):
+            t = torch.tensor(values, dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.tolist()
+
         log = ops.LaunchLog(timed=not args.graphs)
         ops.set_launch_log(log)
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
         runner.stage_events = []
-        e0.record()
-        phase(args.steps, resident)                       # K steps on every rank; K chunks enter, K leave
-        e1.record()
-        barrier()
-        clocks = sampler.stop() if rank == 0 else None
+        first_ms = max_over_ranks([region(resident)])[0]
         ops.set_launch_log(None)
-        ms = e0.elapsed_time(e1)
+        # repeat the region until the regions cover about two seconds (same count on every rank)
+        repeats = max(1, min(args.max_repeats, -(-int(args.min_seconds * 1e3) // max(int(first_ms), 1))))
+        regions = [first_ms] + max_over_ranks([region(resident) for _ in range(repeats - 1)])
+        clocks = sampler.stop() if rank == 0 else None
+        ms = statistics.median(regions)
         stage_ms = statistics.mean(a.elapsed_time(b) for a, b in runner.stage_events)
         runner.stage_events = None
 
-        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # host buffers in, host result out, every step; chunk latency from wall-clock-anchored device events:
+        # rank 0 stamps a chunk's entry, the last rank the arrival of its final denoise level on the host
+        stamps = LatencyStamps()
+        anchor = torch.cuda.Event(enable_timing=True)
+
+        def host_src(i):
+            stamps.enter()
+            return host_chunks[i % n_host].to(device, non_blocking=True)
+
+        def host_sink(out):
+            host_out.copy_(out[-1], non_blocking=True)
+            stamps.leave()
+
         barrier()
-        e2.record()
-        phase(args.steps, lambda i: host_chunks[i % n_host].to(device, non_blocking=True),
-              sink=lambda out: host_out.copy_(out[-1], non_blocking=True))
-        e3.record()
-        barrier()
-        ms_e2e = e2.elapsed_time(e3)
+        anchor.record()
+        anchor.synchronize()
+        anchor_wall = time.time()
+        chunk_at_anchor = chunk[0]
+        regions_e2e = max_over_ranks([region(host_src, host_sink) for _ in range(repeats)])
+        ms_e2e = statistics.median(regions_e2e)
         ops.read_status(device)
+        # wall-clock time (one node, one clock) of every stamp, indexed by this rank's chunk counter
+        n_slots = repeats * args.steps
+        mine = torch.full((2, n_slots), float("nan"), dtype=torch.float64, device=device)
+        for row, evs in ((0, stamps.t_in), (1, stamps.t_out)):
+            for j, ev in enumerate(evs[:n_slots]):
+                mine[row, j] = anchor_wall + anchor.elapsed_time(ev) / 1e3
+        first_chunk = torch.tensor([float(chunk_at_anchor)], dtype=torch.float64, device=device)
+        all_stamps = [torch.zeros_like(mine) for _ in range(world)]
+        all_first = [torch.zeros_like(first_chunk) for _ in range(world)]
+        dist.all_gather(all_stamps, mine)
+        dist.all_gather(all_first, first_chunk)
+        lat = []
+        if rank == 0:
+            t_in, c_in = all_stamps[0][0].tolist(), int(all_first[0].item())
+            t_out, c_out = all_stamps[world - 1][1].tolist(), int(all_first[world - 1].item())
+            # a chunk that enters as chunk c leaves the last stage with its final level as the last row of the
+            # stage batch of chunk c + (levels - 1) * world (it re-enters stage 0 `world` chunks later per level)
+            lag = (rows - 1) * world
+            for j, t0 in enumerate(t_in):
+                k = (c_in + j + lag) - c_out
+                same_region = 0 <= k < n_slots and (j // args.steps) == (k // args.steps)
+                if same_region and t0 == t0 and t_out[k] == t_out[k]:
+                    lat.append((t_out[k] - t0) * 1e3)
 
         tlog = log
         if args.graphs:                    # per-kernel durations: a launch-by-launch pass of the same steps
@@ -534,9 +830,16 @@ def run_pipeline(args):
             "unit": "video frames/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "repeats": repeats, "region_ms": [round(r, 3) for r in regions],
             "e2e": {"value": VIDEO_FRAMES_PER_CHUNK * args.steps / (ms_e2e_max / 1e3), "unit": "video frames/s",
                     "ms_per_step": ms_e2e_max / args.steps, "h2d_bytes_per_step": host_chunks[0].numel() * 2,
-                    "d2h_bytes_per_step": host_out.numel() * 2},
+                    "d2h_bytes_per_step": host_out.numel() * 2, "region_ms": [round(r, 3) for r in regions_e2e]},
+            "latency_ms": {"median": _median(lat), "max": max(lat) if lat else None, "chunks": len(lat),
+                           "definition": "per chunk under back-to-back load: from the enqueue of the chunk's "
+                                         "host->device copy on stage 0 to the completion, on the last stage, of the "
+                                         "device->host copy of its last denoise level; device events anchored to the "
+                                         f"node's wall clock on each rank; the chunk crosses the {world} stages once "
+                                         f"per denoise level ({rows} levels)"},
             "gpu_launches": int(sm[2].item()),
             "roofline": {"kernel": "attn_kvcache (tcgen05)", "bound": "tensor", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
@@ -557,6 +860,13 @@ def main():
                     help="reference: the CPU restatement on the host cores; library: comparison arm, N=1 only, "
                          "the reference's GPU op chain (flash-attn, PyTorch ops) under the same model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true",
+                    help="N=1: skip the reference's GPU path (timed in the same process after this package's own)")
+    ap.add_argument("--reference-steps", type=int, default=6, help="timed chunk steps per reference GPU arm")
+    ap.add_argument("--cpu-budget", type=float, default=150.0, help="--impl reference: seconds of CPU work")
+    ap.add_argument("--min-seconds", type=float, default=2.0,
+                    help="the timed region of K steps is repeated until the regions cover this long; median counts")
+    ap.add_argument("--max-repeats", type=int, default=8)
     ap.add_argument("--no-graphs", dest="graphs", action="store_false",
                     help="launch every op of every step from Python instead of replaying steady steps from a CUDA graph")
     ap.add_argument("--block-split", default="reference", choices=["reference", "balanced"],

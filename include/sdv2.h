@@ -116,6 +116,35 @@ int sdv2_rope_kv_append_indirect(const sdv2_view* q, const sdv2_view* k, const s
                                  int dtype, int* status_dev, void* stream);
 
 /*
+ * The same operation with the RMS norm of q and k folded in: q and k arrive as the raw outputs of
+ * their projections (slices of one fused q|k|v projection are fine: only head_dim and the heads of
+ * a token must be contiguous) and are normalised over the whole token row of heads * head_dim
+ * elements before the rope,
+ *   x_n = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * weight)
+ * which is WanRMSNorm.forward (models/wan/wan_base/modules/model.py:70-86) as applied to the q and k
+ * projections at models/wan/causal_model.py:212-214, with the same intermediate roundings; the row
+ * statistics are summed in the order sdv2_rmsnorm uses, so the result equals sdv2_rmsnorm followed
+ * by sdv2_rope_kv_append bit for bit.  v is copied as it is.
+ * bf16 tensors only; heads * head_dim <= 8192; heads of a token back to back (stride_head ==
+ * head_dim) - otherwise SDV2_ERR_UNSUPPORTED_SHAPE, and the caller runs sdv2_rmsnorm first.
+ * norm_q_weight_dev / norm_k_weight_dev: device bf16 [heads * head_dim], 16-byte aligned.
+ * Slot parameters: either the host arrays start_frame / dst_begin (+ global_end_val / local_end_val)
+ * with step_params_dev NULL, or step_params_dev (device int64 [4][rows], as for
+ * sdv2_rope_kv_append_indirect) with the host arrays NULL.
+ */
+int sdv2_norm_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v,
+                             const sdv2_view* q_out, const sdv2_view* k_cache, const sdv2_view* v_cache,
+                             int rows, int new_tokens, int heads, int head_dim, int64_t cache_tokens,
+                             const double* rope_table_dev, int table_rows,
+                             int grid_f, int grid_h, int grid_w,
+                             const int64_t* start_frame, const int64_t* dst_begin,
+                             const int64_t* step_params_dev,
+                             int64_t* global_end_dev, int64_t* local_end_dev,
+                             const int64_t* global_end_val, const int64_t* local_end_val,
+                             const void* norm_q_weight_dev, const void* norm_k_weight_dev, float norm_eps,
+                             int* status_dev, void* stream);
+
+/*
  * Attention of the new queries over the wrapped cache: out[b] = softmax(q[b] k[b,:L_b]^T * scale)
  * v[b,:L_b] with L_b = seq_lens[b], no causal or window mask (the window is the cache content).
  *

@@ -1,23 +1,26 @@
 """Micro-benchmark of the cache kernels on synthetic bf16 q/k/v ~ N(0,1) (seed 0).
 
-    python -m streamdiffusionv2_b200.kernel_bench --kernel append --rows 2 --heads 12
-    python -m streamdiffusionv2_b200.kernel_bench --kernel attn --rows 1 --heads 12 --window-frames 21
-    python -m streamdiffusionv2_b200.kernel_bench --sweep            # window x heads x rows x chunk grid
+    python kernel_bench.py --kernel append --rows 2 --heads 12
+    python kernel_bench.py --kernel attn --rows 1 --heads 12 --window-frames 21
+    python kernel_bench.py --sweep            # window x heads x rows x chunk grid
+    python kernel_bench.py --library-baselines   # what the reference executes on a GPU for the same steps
 
 Prints one JSON line per configuration: time per launch (CUDA events on the launching stream,
 L2 flushed between launches by writing a 256 MB buffer), append GB/s (6 x rows x tokens x heads x
 128 x 2 bytes per launch) and attention TFLOP/s (4 x tokens x 128 x heads x sum of cache lengths).
-`--check-index-run STEPS` additionally drives the slot state for STEPS chunks with the drivers'
-refresh rule and compares the device index tensors with the host mirror at every step.
+A measurement script: it is not part of the package and the package never imports it.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
 import statistics
 import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 FRAME_TOKENS = 1560
 
@@ -40,8 +43,8 @@ def _time(fn, iters, warmup, flush):
 
 
 def run_config(kernel, rows, heads, window_frames, chunk_frames, iters, warmup, flush_l2=True):
-    from . import ops
-    from .wan_model import build_rope_table
+    from streamdiffusionv2_b200 import ops
+    from streamdiffusionv2_b200.wan_model import build_rope_table
     dev = torch.device("cuda")
     D = 128
     n = chunk_frames * FRAME_TOKENS
@@ -86,7 +89,7 @@ def library_baselines(rows, heads, window_frames, chunk_frames, iters, warmup):
     321-322), and flash_attn_with_kvcache (:353-358) or, failing that, PyTorch SDPA (:111-157).
     Library calls only - nothing here is part of the product path."""
     import torch.nn.functional as F
-    from .wan_model import build_rope_table
+    from streamdiffusionv2_b200.wan_model import build_rope_table
     dev = torch.device("cuda")
     D, n, s = 128, chunk_frames * FRAME_TOKENS, window_frames * FRAME_TOKENS
     q, k, v = (torch.randn(rows, n, heads, D, device=dev, dtype=torch.bfloat16) for _ in range(3))
@@ -133,46 +136,6 @@ def library_baselines(rows, heads, window_frames, chunk_frames, iters, warmup):
     return res
 
 
-def check_index_run(rows, heads, window_frames, chunk_frames, steps):
-    """Long wraparound run of the slot logic through the append kernel: device index tensors must
-    equal the host mirror after every step, and every slot must stay inside the cache."""
-    from . import ops
-    from .ring_state import RingState
-    from .wan_model import build_rope_table
-    dev = torch.device("cuda")
-    D, n, s = 128, chunk_frames * FRAME_TOKENS, window_frames * FRAME_TOKENS
-
-    class Mod:
-        sink_size, adapt_sink_thr, evict_idx = 1, -1, None
-
-    mod = Mod()
-    kv = {"k": torch.zeros(rows, s, heads, D, dtype=torch.bfloat16, device=dev),
-          "v": torch.zeros(rows, s, heads, D, dtype=torch.bfloat16, device=dev),
-          "global_end_index": torch.zeros(rows, dtype=torch.long, device=dev),
-          "local_end_index": torch.zeros(rows, dtype=torch.long, device=dev), "total_steps": 1, "current_step": 1}
-    table = ops.rope_table_device(build_rope_table(D), dev)
-    q = torch.randn(rows, n, heads, D, device=dev, dtype=torch.bfloat16)
-    start, bad = 0, 0
-    history = [0] * rows
-    for step in range(steps):
-        if start // FRAME_TOKENS >= 50:
-            start = s - FRAME_TOKENS
-        history = [start] + history[:-1]
-        st = RingState.of(kv)
-        dst, lens = st.plan(kv, mod, history, n, FRAME_TOKENS)
-        ops.rope_kv_append(q, q, q, kv["k"], kv["v"], table, (chunk_frames, 30, 52),
-                           [h // FRAME_TOKENS for h in history], dst,
-                           index_tensors=(kv["global_end_index"], kv["local_end_index"]),
-                           index_values=(st.global_end, st.local_end))
-        if step % 50 == 49 or step == steps - 1:
-            if kv["global_end_index"].tolist() != st.global_end or kv["local_end_index"].tolist() != st.local_end:
-                bad += 1
-        start += n
-    ops.read_status(dev)
-    return {"check": "index_run", "rows": rows, "window_frames": window_frames, "chunk_frames": chunk_frames,
-            "steps": steps, "mismatches": bad}
-
-
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="attn", choices=["append", "attn", "cross"])
@@ -184,14 +147,10 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--sweep", action="store_true")
-    ap.add_argument("--check-index-run", type=int, default=0)
     ap.add_argument("--library-baselines", action="store_true")
     a = ap.parse_args(argv)
     if a.library_baselines:
         print(json.dumps(library_baselines(a.rows, a.heads, a.window_frames, a.chunk_frames, a.iters, a.warmup)))
-        return
-    if a.check_index_run:
-        print(json.dumps(check_index_run(a.rows, a.heads, a.window_frames, a.chunk_frames, a.check_index_run)))
         return
     if not a.sweep:
         print(json.dumps(run_config(a.kernel, a.rows, a.heads, a.window_frames, a.chunk_frames, a.iters, a.warmup,

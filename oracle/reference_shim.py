@@ -79,13 +79,19 @@ def set_flash_attn(ref, enabled: bool) -> None:
 
 def build_reference_pipeline(ref, model_kw: dict, levels, frame_seq_length: int, cache_frames: int, sink: int,
                              frames_per_chunk: int, prompt: torch.Tensor, device="cpu", dtype=torch.float32,
-                             init_parameters=None):
+                             init_parameters=None, construct_on_device: bool = False):
     """The reference's CausalWanModel + CausalWanDiffusionWrapper + CausalStreamInferencePipeline,
     constructed without their checkpoint / text-encoder / VAE loading (object.__new__ plus the
     attributes their __init__ would set: models/wan/causal_stream_inference.py:37-70,
-    models/wan/wan_wrapper.py:161-169).  `init_parameters(model)` seeds the weights."""
+    models/wan/wan_wrapper.py:161-169).  `init_parameters(model)` seeds the weights;
+    `construct_on_device` creates the parameters on `device` directly (a billion-parameter model
+    takes a while to initialise on the host)."""
     device = torch.device(device)
-    model = ref.cm.CausalWanModel(**model_kw)
+    if construct_on_device:
+        with torch.device(device):
+            model = ref.cm.CausalWanModel(**model_kw)
+    else:
+        model = ref.cm.CausalWanModel(**model_kw)
     if init_parameters is not None:
         init_parameters(model)
     model = model.to(device=device, dtype=dtype).eval()

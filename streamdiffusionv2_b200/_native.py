@@ -44,6 +44,13 @@ _SIGNATURES = {
                                                                         C.c_int64, C.c_void_p, C.c_int, C.c_int,
                                                                         C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                                         C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "sdv2_norm_rope_kv_append": (C.c_int, [C.POINTER(View)] * 6 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64,
+                                                                    C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                                    C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                                                    C.c_void_p, C.c_void_p, C.c_void_p,
+                                                                    C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                                                    C.c_void_p, C.c_void_p, C.c_float,
+                                                                    C.c_void_p, C.c_void_p]),
     "sdv2_attn_kvcache": (C.c_int, [C.POINTER(View)] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64,
                                                              C.POINTER(C.c_int32), C.c_float, C.c_void_p,
                                                              C.c_size_t, C.c_void_p]),

@@ -93,10 +93,12 @@ def _adaptive_front(kv_cache, roped_k, v, i, sink_size, frame_tokens, thr) -> Op
     return None
 
 
-def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_start):
+def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_start, norm=None):
     """Rope, slot write, index update and attention for already projected q/k/v [B, N, H, D].
     Returns the attention output [B, N, H, D].  This is the part of the reference forward between
-    the qkv projection and the output projection (causal_model.py:250-384)."""
+    the qkv projection and the output projection (causal_model.py:250-384).  With `norm` =
+    (weight_q, weight_k, eps) q and k are the raw projections and their RMS norm
+    (causal_model.py:212-214) runs inside the append launch."""
     B, n_new, H, D = q.shape
     f, gh, gw = (int(x) for x in grid_sizes[0].tolist())
     frame_tokens = gh * gw
@@ -115,7 +117,7 @@ def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_
         raise RuntimeError("the adaptive sink test reads the device back and cannot be recorded in a graph")
     if not adaptive:
         dst, seq_lens = state.plan(kv_cache, attn_module, starts, n_new, frame_tokens)
-        extra = {}
+        extra = {} if norm is None else {"norm": norm}
         if _step_recorder is not None:
             extra["step_params"] = _step_recorder.layer_params(attn_module, kv_cache, start_frames, dst, state,
                                                                seq_lens, n_new, frame_tokens)
@@ -127,7 +129,8 @@ def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_
         # staging chunk first, then test and place row by row
         stage_k = torch.empty_like(k, memory_format=torch.contiguous_format)
         stage_v = torch.empty_like(v, memory_format=torch.contiguous_format)
-        roped_q = ops.rope_kv_append(q, k, v, stage_k, stage_v, table, (f, gh, gw), start_frames, [0] * B)
+        roped_q = ops.rope_kv_append(q, k, v, stage_k, stage_v, table, (f, gh, gw), start_frames, [0] * B,
+                                     **({} if norm is None else {"norm": norm}))
         state._ensure_queues(kv_cache, attn_module)
         seq_lens = []
         for i in range(B):
@@ -171,6 +174,53 @@ def _qk_norm(norm, x: torch.Tensor) -> torch.Tensor:
     return norm(x)
 
 
+def _is_rms(norm) -> bool:
+    w = getattr(norm, "weight", None)
+    return w is not None and type(norm).__name__.endswith("RMSNorm") and hasattr(norm, "eps")
+
+
+def _fused_qkv_weights(attn):
+    """[3 * dim, dim] weight and [3 * dim] bias of the q | k | v projections of an attention module,
+    concatenated once and kept on the module (`_sdv2_qkv`); rebuilt when any of the six parameters was
+    replaced or written (identity, address, version counter).  The parameters themselves stay as
+    they are, so checkpoints load and save unchanged."""
+    lins = (attn.q, attn.k, attn.v)
+    ps = [p for l in lins for p in (l.weight, l.bias)]
+    key = tuple((id(p), p.data_ptr(), p._version) if p is not None else None for p in ps)
+    hit = getattr(attn, "_sdv2_qkv", None)
+    if hit is not None and hit[0] == key:
+        return hit[1], hit[2]
+    with torch.no_grad():
+        w = torch.cat([l.weight for l in lins], dim=0).contiguous()
+        b = None if any(l.bias is None for l in lins) else torch.cat([l.bias for l in lins], dim=0).contiguous()
+    attn._sdv2_qkv = (key, w, b)
+    return w, b
+
+
+def project_qkv(attn, x):
+    """q, k, v [b, s, n, d] of a self-attention module plus the norm still to be applied.
+    On CUDA in bf16: one GEMM over the concatenated q | k | v weight, q / k / v are slices of its
+    output, and when the q and k norms are RMS norms that the append kernel can fold in, they are
+    returned as (weight_q, weight_k, eps) instead of being run.  Elsewhere: the module's own three
+    projections and norms, as the reference runs them (causal_model.py:212-218)."""
+    b, s, n, d = *x.shape[:2], attn.num_heads, attn.head_dim
+    plain = all(type(l) is torch.nn.Linear for l in (attn.q, attn.k, attn.v))
+    if _fusable(x) and plain and attn.q.weight.dtype == torch.bfloat16:
+        w, bias = _fused_qkv_weights(attn)
+        qkv = torch.nn.functional.linear(x, w, bias).view(b, s, 3, n, d)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        if (_is_rms(attn.norm_q) and _is_rms(attn.norm_k) and attn.norm_q.eps == attn.norm_k.eps
+                and ops.can_fuse_norm(q, k, v, attn.norm_q.weight, attn.norm_k.weight)):
+            return q, k, v, (attn.norm_q.weight, attn.norm_k.weight, attn.norm_q.eps)
+        q = _qk_norm(attn.norm_q, q.reshape(b, s, n * d)).view(b, s, n, d)
+        k = _qk_norm(attn.norm_k, k.reshape(b, s, n * d)).view(b, s, n, d)
+        return q, k, v, None
+    q = _qk_norm(attn.norm_q, attn.q(x)).view(b, s, n, d)
+    k = _qk_norm(attn.norm_k, attn.k(x)).view(b, s, n, d)
+    v = attn.v(x).view(b, s, n, d)
+    return q, k, v, None
+
+
 def self_attention_forward(self, x, seq_lens, grid_sizes, freqs, block_mask, kv_cache=None, current_start=0,
                            current_end=0, causal_rope_cache=None):
     """Drop-in for CausalWanSelfAttention.forward on the kv-cache path (the training branch, which
@@ -180,11 +230,8 @@ def self_attention_forward(self, x, seq_lens, grid_sizes, freqs, block_mask, kv_
         if original is None:
             raise RuntimeError("the kernel-backed self-attention serves the kv-cache path only")
         return original(x, seq_lens, grid_sizes, freqs, block_mask)
-    b, s, n, d = *x.shape[:2], self.num_heads, self.head_dim
-    q = _qk_norm(self.norm_q, self.q(x)).view(b, s, n, d)
-    k = _qk_norm(self.norm_k, self.k(x)).view(b, s, n, d)
-    v = self.v(x).view(b, s, n, d)
-    out = cached_attention(self, q, k, v, grid_sizes, freqs, kv_cache, current_start)
+    q, k, v, norm = project_qkv(self, x)
+    out = cached_attention(self, q, k, v, grid_sizes, freqs, kv_cache, current_start, norm=norm)
     return self.o(out.flatten(2))
 
 

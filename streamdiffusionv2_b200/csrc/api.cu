@@ -192,7 +192,9 @@ static int append_common(const sdv2_view* q, const sdv2_view* k, const sdv2_view
                          int grid_f, int grid_h, int grid_w, const int64_t* start_frame,
                          const int64_t* dst_begin, int64_t* global_end_dev, int64_t* local_end_dev,
                          const int64_t* global_end_val, const int64_t* local_end_val,
-                         const int64_t* step_params_dev, int dtype, int* status_dev, void* stream) {
+                         const int64_t* step_params_dev, int dtype, int* status_dev, void* stream,
+                         const void* norm_q_weight_dev = nullptr, const void* norm_k_weight_dev = nullptr,
+                         float norm_eps = 0.f) {
   if (rows <= 0 || new_tokens <= 0 || heads <= 0 || cache_tokens <= 0 || table_rows <= 0) return SDV2_ERR_INVALID_ARG;
   if (grid_f <= 0 || grid_h <= 0 || grid_w <= 0) return SDV2_ERR_INVALID_ARG;
   if (static_cast<int64_t>(grid_f) * grid_h * grid_w != new_tokens) return SDV2_ERR_INVALID_ARG;
@@ -213,9 +215,18 @@ static int append_common(const sdv2_view* q, const sdv2_view* k, const sdv2_view
   for (const sdv2_view* vw : views)
     if ((rc = check_view(vw, esize, false)) != SDV2_OK) return rc;
   if (grid_h > table_rows || grid_w > table_rows) return SDV2_ERR_INVALID_ARG;
+  if ((norm_q_weight_dev == nullptr) != (norm_k_weight_dev == nullptr)) return SDV2_ERR_INVALID_ARG;
+  if (norm_q_weight_dev != nullptr) {
+    if (dtype != SDV2_DTYPE_BF16) return SDV2_ERR_UNSUPPORTED_SHAPE;
+    if (!aligned16(norm_q_weight_dev) || !aligned16(norm_k_weight_dev)) return SDV2_ERR_MISALIGNED;
+    if (!(norm_eps >= 0.f) || !isfinite(norm_eps)) return SDV2_ERR_INVALID_ARG;
+  }
 
   sdv2::AppendParams p;
   memset(&p, 0, sizeof(p));
+  p.norm_q_weight = norm_q_weight_dev;
+  p.norm_k_weight = norm_k_weight_dev;
+  p.norm_eps = norm_eps;
   for (int b = 0; b < rows && !indirect; ++b) {
     // the reference fails with a shape mismatch where these hold; fail loudly instead of writing
     // outside the cache or reading past the rope table
@@ -247,7 +258,23 @@ static int append_common(const sdv2_view* q, const sdv2_view* k, const sdv2_view
   p.grid_f = grid_f;
   p.status = status_dev;
   cudaError_t e = sdv2::launch_rope_kv_append(p, dtype, static_cast<cudaStream_t>(stream));
+  if (e == cudaErrorNotSupported) return SDV2_ERR_UNSUPPORTED_SHAPE;
   return e == cudaSuccess ? SDV2_OK : cuda_fail(e);
+}
+
+int sdv2_norm_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, const sdv2_view* q_out,
+                             const sdv2_view* k_cache, const sdv2_view* v_cache, int rows, int new_tokens, int heads,
+                             int head_dim, int64_t cache_tokens, const double* rope_table_dev, int table_rows,
+                             int grid_f, int grid_h, int grid_w, const int64_t* start_frame,
+                             const int64_t* dst_begin, const int64_t* step_params_dev, int64_t* global_end_dev,
+                             int64_t* local_end_dev, const int64_t* global_end_val, const int64_t* local_end_val,
+                             const void* norm_q_weight_dev, const void* norm_k_weight_dev, float norm_eps,
+                             int* status_dev, void* stream) {
+  if (norm_q_weight_dev == nullptr || norm_k_weight_dev == nullptr) return SDV2_ERR_INVALID_ARG;
+  return append_common(q, k, v, q_out, k_cache, v_cache, rows, new_tokens, heads, head_dim, cache_tokens,
+                       rope_table_dev, table_rows, grid_f, grid_h, grid_w, start_frame, dst_begin, global_end_dev,
+                       local_end_dev, global_end_val, local_end_val, step_params_dev, SDV2_DTYPE_BF16, status_dev,
+                       stream, norm_q_weight_dev, norm_k_weight_dev, norm_eps);
 }
 
 int sdv2_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, const sdv2_view* q_out,

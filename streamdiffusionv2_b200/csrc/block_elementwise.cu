@@ -67,11 +67,11 @@ __global__ void __launch_bounds__(kRowThreads) row_norm_kernel(const __grid_cons
     if (c < n_vec) {
       v[i] = xr[c];
       const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+      if (kLayerNorm) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = lo_f(w[j]), b = hi_f(w[j]);
-        s += a + b;
-        ss += a * a + b * b;
+        for (int j = 0; j < 4; ++j) s += lo_f(w[j]) + hi_f(w[j]);
+      } else {
+        ss = rms_accumulate(ss, v[i]);     // shared with the append kernel's fused q/k norm
       }
     }
   }
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kRowThreads) row_norm_kernel(const __grid_cons
     }
     rstd = rsqrtf(block_sum(d2, red) / p.dim + p.eps);
   } else {
-    rstd = rsqrtf(block_sum(ss, red) / p.dim + p.eps);
+    rstd = rms_rstd(block_sum(ss, red), p.dim, p.eps);
   }
   const uint4* mul = nullptr;
   const uint4* add = nullptr;
@@ -123,6 +123,10 @@ __global__ void __launch_bounds__(kRowThreads) row_norm_kernel(const __grid_cons
       uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
+        if (!kLayerNorm) {
+          o[j] = rms_scale_pair(w[j], rstd, m[j]);
+          continue;
+        }
         float lo = bf16_round((lo_f(w[j]) - mean) * rstd);
         float hi = bf16_round((hi_f(w[j]) - mean) * rstd);
         const float ml = kLayerNorm ? bf16_round(1.f + lo_f(m[j])) : lo_f(m[j]);   // (1 + scale) is a bf16 op upstream

@@ -51,6 +51,12 @@ struct Vec<__nv_bfloat16> {
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
   }
+  // RMS-normalise first (bf16(bf16(x * rstd) * weight), the roundings of the unfused norm), then rope
+  __device__ __forceinline__ static uint4 rope_normed(uint4 x, const double2 (&cs)[4], float rstd, uint4 wv) {
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    return rope(make_uint4(rms_scale_pair(x.x, rstd, ww[0]), rms_scale_pair(x.y, rstd, ww[1]),
+                           rms_scale_pair(x.z, rstd, ww[2]), rms_scale_pair(x.w, rstd, ww[3])), cs);
+  }
 };
 
 template <>
@@ -63,6 +69,9 @@ struct Vec<float> {
     rope_pair(static_cast<double>(__uint_as_float(x.z)), static_cast<double>(__uint_as_float(x.w)), cs[1],
               re1, im1);
     return make_uint4(__float_as_uint(re0), __float_as_uint(im0), __float_as_uint(re1), __float_as_uint(im1));
+  }
+  __device__ __forceinline__ static uint4 rope_normed(uint4 x, const double2 (&cs)[2], float, uint4) {
+    return rope(x, cs);  // the fused norm exists for bf16 only; the launcher never asks for it here
   }
 };
 
@@ -176,10 +185,24 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 }
 
 // Stage layout: q rows | k rows | v rows (tile_tokens x row_bytes each) | multiplier rows
-// (tile_tokens x half complex doubles).  The producer group (the last warps) issues the bulk copies
+// (tile_tokens x half complex doubles) | with kNorm: 1 / rms of every q row, then of every k row.  The producer group (the last warps) issues the bulk copies
 // of a tile and builds the tile's multiplier rows from the rope table; each of its warps then
 // arrives on the stage's "full" barrier, which completes once the copied bytes are in as well.
-template <typename T>
+// Barrier over `threads` threads (a multiple of 32) that also ANDs a flag over them.
+__device__ __forceinline__ bool named_barrier_and(int id, int threads, bool flag) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %3, 0;\n\t"
+      "bar.red.and.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(flag))
+      : "memory");
+  return r != 0;
+}
+
+template <typename T, bool kNorm>
 __global__ void __launch_bounds__((staged::kMaxConsumerWarps + staged::kProducerWarps) * 32, 1)
 rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
   using namespace staged;
@@ -298,8 +321,37 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
       const int s = i % kStages;
       bool ok = mbar_wait(bar0 + 8 * s, (i / kStages) & 1, abort_flag, p.status, WAIT_KV_FULL);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!kNorm && !ok) break;
       const uint8_t* sq = gbase + s * stage_bytes;
+      const float* rstd_s = reinterpret_cast<const float*>(sq + mult_off + tile_tokens * mult_row_bytes);
+      if (kNorm) {
+        // 1 / rms of every staged q and k row, one warp per row, summed in the order sdv2_rmsnorm uses
+        float* rstd_w = const_cast<float*>(rstd_s);
+        for (int r = warp; ok && r < 2 * n; r += consumer_warps) {
+          const int which = r >= n ? 1 : 0;
+          const uint8_t* rowp = sq + which * tensor_stride + (r - which * n) * row_bytes;
+          float g[8];
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            float ss = 0.f;
+            if (w * 32 < row_vecs) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int c = w * 32 + lane + i * 256;
+                if (c < row_vecs) ss = rms_accumulate(ss, *reinterpret_cast<const uint4*>(rowp + c * 16));
+              }
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            }
+            g[w] = ss;
+          }
+          if (lane == 0) rstd_w[r] = rms_rstd(rms_fold_groups(g), p.heads * p.head_dim, p.norm_eps);
+        }
+        // consumers only (the producer group never joins); a warp whose wait was abandoned still
+        // arrives, and everybody leaves together
+        ok = named_barrier_and(1, consumers, ok);
+        if (!ok) break;
+      }
       const int n_vec = n * row_vecs;
       const int64_t slot0 = row_dst_begin(p, b) + t0;
       T* qo_base = static_cast<T*>(p.q_out.ptr) + b * p.q_out.stride_row + t0 * p.q_out.stride_tok;
@@ -320,8 +372,18 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
         const uint4 vv = *reinterpret_cast<const uint4*>(sq + 2 * tensor_stride + off);
         const int e0 = c * kElems;
         *reinterpret_cast<uint4*>(vc_base + j * p.v_cache.stride_tok + h * p.v_cache.stride_head + e0) = vv;
-        *reinterpret_cast<uint4*>(qo_base + j * p.q_out.stride_tok + h * p.q_out.stride_head + e0) = Vec<T>::rope(qv, cs);
-        *reinterpret_cast<uint4*>(kc_base + j * p.k_cache.stride_tok + h * p.k_cache.stride_head + e0) = Vec<T>::rope(kv, cs);
+        uint4 qr, kr;
+        if (kNorm) {
+          const uint4 wq = __ldg(reinterpret_cast<const uint4*>(p.norm_q_weight) + rv);
+          const uint4 wk = __ldg(reinterpret_cast<const uint4*>(p.norm_k_weight) + rv);
+          qr = Vec<T>::rope_normed(qv, cs, rstd_s[j], wq);
+          kr = Vec<T>::rope_normed(kv, cs, rstd_s[n + j], wk);
+        } else {
+          qr = Vec<T>::rope(qv, cs);
+          kr = Vec<T>::rope(kv, cs);
+        }
+        *reinterpret_cast<uint4*>(qo_base + j * p.q_out.stride_tok + h * p.q_out.stride_head + e0) = qr;
+        *reinterpret_cast<uint4*>(kc_base + j * p.k_cache.stride_tok + h * p.k_cache.stride_head + e0) = kr;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar0 + 8 * (kStages + s));
@@ -333,13 +395,13 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
 
 static uint32_t magic_of(uint32_t d) { return static_cast<uint32_t>(((1ull << 32) + d - 1) / d); }
 
-template <typename T>
+template <typename T, bool kNorm>
 static cudaError_t launch_staged(const AppendParams& p, int device, int grid, int threads, uint32_t smem,
                                  cudaStream_t stream) {
   static DynamicSmemGrant smem_grant;  // one per instantiation
-  cudaError_t e = smem_grant.ensure(rope_kv_append_staged_kernel<T>, static_cast<int>(smem), device);
+  cudaError_t e = smem_grant.ensure(rope_kv_append_staged_kernel<T, kNorm>, static_cast<int>(smem), device);
   if (e != cudaSuccess) return e;
-  rope_kv_append_staged_kernel<T><<<grid, threads, smem, stream>>>(p);
+  rope_kv_append_staged_kernel<T, kNorm><<<grid, threads, smem, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -360,16 +422,19 @@ cudaError_t launch_rope_kv_append(const AppendParams& p_in, int dtype, cudaStrea
   const bool div_ok = static_cast<uint64_t>(p.tokens) * p.plane < (1ull << 32) &&
                       static_cast<uint64_t>(staged::kMaxTileTokens) * row_vecs * row_vecs < (1ull << 32);
   if (!div_ok || vph > 256 || vph < 1) return cudaErrorInvalidValue;
+  if (p.norm_q_weight != nullptr && (dtype != SDV2_DTYPE_BF16 || row_vecs > 1024)) return cudaErrorNotSupported;
 
   const bool rows_contiguous = p.q.stride_head == p.head_dim && p.k.stride_head == p.head_dim &&
                                p.v.stride_head == p.head_dim;
   // tile size and consumer-warp count: the tile's vectors should split evenly over the consumer
   // threads and three stages must fit in shared memory; then more warps and larger tiles
   const uint32_t mult_row = static_cast<uint32_t>(p.half) * 16u;
+  const bool norm = p.norm_q_weight != nullptr;
+  const uint32_t norm_row = norm ? 8u : 0u;   // two floats per token: 1 / rms of its q row and of its k row
   int best_tt = 0, best_w = 0;
   double best_score = 0.0;
   for (int tt = 1; tt <= staged::kMaxTileTokens; ++tt) {
-    const uint32_t stage = (3u * tt * row_bytes + tt * mult_row + 127u) & ~127u;
+    const uint32_t stage = (3u * tt * row_bytes + tt * (mult_row + norm_row) + 127u) & ~127u;
     if (static_cast<uint64_t>(stage) * staged::kStagesWanted + staged::kTailBytes > staged::kSmemLimit) break;
     for (int w = staged::kMinConsumerWarps; w <= staged::kMaxConsumerWarps; ++w) {
       const int n_vec = tt * row_vecs, thr = 32 * w;
@@ -385,7 +450,7 @@ cudaError_t launch_rope_kv_append(const AppendParams& p_in, int dtype, cudaStrea
   }
   if (rows_contiguous && best_tt >= 1) {
     p.tile_tokens = best_tt;
-    p.stage_bytes = (3u * best_tt * row_bytes + best_tt * mult_row + 127u) & ~127u;
+    p.stage_bytes = (3u * best_tt * row_bytes + best_tt * (mult_row + norm_row) + 127u) & ~127u;
     p.stages = staged::kStagesWanted;
     const uint32_t smem = p.stages * p.stage_bytes + staged::kTailBytes;
     DeviceInfo di;
@@ -394,9 +459,11 @@ cudaError_t launch_rope_kv_append(const AppendParams& p_in, int dtype, cudaStrea
     const int64_t total = static_cast<int64_t>(p.rows) * p.tokens;
     const int grid = static_cast<int>(total < di.sms ? total : di.sms);
     const int threads = (best_w + staged::kProducerWarps) * 32;
-    return dtype == SDV2_DTYPE_BF16 ? launch_staged<__nv_bfloat16>(p, di.device, grid, threads, smem, stream)
-                                    : launch_staged<float>(p, di.device, grid, threads, smem, stream);
+    if (norm) return launch_staged<__nv_bfloat16, true>(p, di.device, grid, threads, smem, stream);
+    return dtype == SDV2_DTYPE_BF16 ? launch_staged<__nv_bfloat16, false>(p, di.device, grid, threads, smem, stream)
+                                    : launch_staged<float, false>(p, di.device, grid, threads, smem, stream);
   }
+  if (norm) return cudaErrorNotSupported;   // the per-vector kernel has no row statistics
   const int tok_per_block = 256 / vph;
   dim3 grid((p.tokens + tok_per_block - 1) / tok_per_block, p.heads, p.rows);
   if (dtype == SDV2_DTYPE_BF16)

@@ -30,12 +30,19 @@ struct AppendParams {
   const int64_t* step_dev;
   int64_t cache_tokens;     // bounds for the device-resident parameters
   int table_rows, grid_f;
+  // optional RMS norm of q and k over the whole token row (heads * head_dim elements) in front of
+  // the rope: bf16 weights [heads * head_dim], or null for no norm (bf16 tensors only)
+  const void* norm_q_weight;
+  const void* norm_k_weight;
+  float norm_eps;
+  uint32_t norm_bytes;      // per-stage bytes for the row statistics (staged kernel)
   int64_t start_frame[SDV2_MAX_ROWS];
   int64_t dst_begin[SDV2_MAX_ROWS];
   int64_t global_end_val[SDV2_MAX_ROWS];
   int64_t local_end_val[SDV2_MAX_ROWS];
 };
 
+// Returns cudaErrorNotSupported when a norm is requested for a layout the staged kernel cannot take.
 cudaError_t launch_rope_kv_append(const AppendParams& p, int dtype, cudaStream_t stream);
 
 struct AttnParams {
@@ -106,6 +113,37 @@ class DynamicSmemGrant {
   std::mutex mu_;
   int granted_[kMaxDevices] = {};
 };
+
+#ifdef __CUDACC__
+// RMS statistics shared by sdv2_rmsnorm and the append kernel's fused q/k norm, so that the two
+// produce the same bits: a row of n_vec 16-byte vectors is summed as 256 "thread" partials (vector
+// c goes to thread c % 256, in ascending order, squares added with fused multiply-adds in element
+// order), each group of 32 threads is folded with an xor butterfly (16, 8, 4, 2, 1), and the 8
+// group sums with the tree ((g0+g4)+(g2+g6)) + ((g1+g5)+(g3+g7)).
+__device__ __forceinline__ float rms_accumulate(float ss, uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xFFFF0000u);
+    ss = __fmaf_rn(a, a, ss);
+    ss = __fmaf_rn(b, b, ss);
+  }
+  return ss;
+}
+__device__ __forceinline__ float rms_fold_groups(const float (&g)[8]) {
+  return ((g[0] + g[4]) + (g[2] + g[6])) + ((g[1] + g[5]) + (g[3] + g[7]));
+}
+__device__ __forceinline__ float rms_rstd(float sum_sq, int dim, float eps) { return rsqrtf(sum_sq / dim + eps); }
+// bf16(bf16(x * rstd) * weight) for the two halves of a packed bf16 pair
+__device__ __forceinline__ uint32_t rms_scale_pair(uint32_t x, float rstd, uint32_t w) {
+  uint32_t t, o;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(t) : "f"(__uint_as_float(x & 0xFFFF0000u) * rstd),
+      "f"(__uint_as_float(x << 16) * rstd));
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o) : "f"(__uint_as_float(t & 0xFFFF0000u) * __uint_as_float(w & 0xFFFF0000u)),
+      "f"(__uint_as_float(t << 16) * __uint_as_float(w << 16)));
+  return o;
+}
+#endif
 
 // Records a failing CUDA call for sdv2_last_cuda_error() and returns SDV2_ERR_CUDA.
 int record_cuda_error(cudaError_t e);

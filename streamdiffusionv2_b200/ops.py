@@ -101,7 +101,8 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
                    q_out: Optional[torch.Tensor] = None,
                    index_tensors: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                    index_values: Optional[Tuple[Sequence[int], Sequence[int]]] = None,
-                   step_params: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   step_params: Optional[torch.Tensor] = None,
+                   norm: Optional[Tuple[torch.Tensor, torch.Tensor, float]] = None) -> torch.Tensor:
     """Rope q and k, write k/v of every row into cache slot [dst_begin[b], dst_begin[b]+N).
     q, k, v: [B, N, H, D]; caches [B, Smax, H, D]; table: float64 [rows, D/2, 2] on the device.
     Optionally stores index_values into the (global_end, local_end) int64 device tensors.
@@ -109,6 +110,9 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
     local ends) the kernel reads those values from that tensor when it runs and the host-side
     start_frames / dst_begin / index_values arguments are ignored: the launch then carries nothing
     that changes from step to step and can be replayed from a CUDA graph.
+    With `norm` = (weight_q, weight_k, eps), q and k are the raw projection outputs and are RMS
+    normalised over the token row in the same launch (see `can_fuse_norm`); the result equals
+    `rmsnorm` followed by this function bit for bit.
     Returns the roped q ([B, N, H, D], contiguous)."""
     B, n_new, H, D = q.shape
     if q_out is None:
@@ -126,6 +130,22 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
         if step_params is None:
             ge_val, le_val = N.i64_array(index_values[0]), N.i64_array(index_values[1])
     views = [N.view(t) for t in (q, k, v, q_out, k_cache, v_cache)]
+    if step_params is not None and (step_params.dtype != torch.int64 or not step_params.is_contiguous()
+                                    or step_params.numel() != 4 * B or step_params.device != q.device):
+        raise ValueError("step_params must be a contiguous int64 [4, rows] tensor on the same device")
+    if norm is not None:
+        wq, wk, eps = norm
+        if not can_fuse_norm(q, k, v, wq, wk):
+            raise ValueError("this layout cannot take the fused norm: apply rmsnorm first")
+        host = step_params is None
+        with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
+            rc = N.lib().sdv2_norm_rope_kv_append(
+                *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
+                f, h, w, N.i64_array(start_frames) if host else None, N.i64_array(dst_begin) if host else None,
+                None if host else step_params.data_ptr(), ge_dev, le_dev, ge_val, le_val,
+                wq.data_ptr(), wk.data_ptr(), float(eps), workspace(q.device).data_ptr(), N.stream_ptr(q.device))
+        N.check(rc, "sdv2_norm_rope_kv_append")
+        return q_out
     if step_params is not None:
         if (step_params.dtype != torch.int64 or not step_params.is_contiguous() or step_params.numel() != 4 * B
                 or step_params.device != q.device):
@@ -144,6 +164,23 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
             N.dtype_code(q.dtype), workspace(q.device).data_ptr(), N.stream_ptr(q.device))
     N.check(rc, "sdv2_rope_kv_append")
     return q_out
+
+
+def can_fuse_norm(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, weight_q: torch.Tensor,
+                  weight_k: torch.Tensor) -> bool:
+    """Whether `rope_kv_append(norm=...)` serves these tensors: bf16 on CUDA, the heads of a token back
+    to back (slices of a fused q|k|v projection qualify), a token row of at most 8192 elements that
+    still fits the kernel's staging buffers, bf16 weights of the row's length."""
+    B, n_new, H, D = q.shape
+    dim = H * D
+    if not (q.is_cuda and q.dtype == torch.bfloat16 and weight_q.dtype == torch.bfloat16
+            and weight_k.dtype == torch.bfloat16 and weight_q.numel() == dim and weight_k.numel() == dim):
+        return False
+    if dim > 8192 or 3 * 3 * dim * 2 + 3 * (D // 2) * 16 > 200 * 1024:        # three stages of one token each
+        return False
+    return (all(t.stride(3) == 1 and t.stride(2) == D for t in (q, k, v))
+            and weight_q.is_contiguous() and weight_k.is_contiguous()
+            and weight_q.data_ptr() % 16 == 0 and weight_k.data_ptr() % 16 == 0)
 
 
 def attn_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: Sequence[int], *,

@@ -13,7 +13,8 @@ def install(monkeypatch):
         return freqs
 
     def rope_kv_append(q, k, v, k_cache, v_cache, table, grid, start_frames, dst_begin, *, q_out=None,
-                       index_tensors=None, index_values=None):
+                       index_tensors=None, index_values=None, norm=None):
+        assert norm is None, "the fused norm is a CUDA bf16 path; CPU runs apply the module's own norms"
         rq = orc.rope_apply(q, grid, table, start_frames).type_as(v)
         rk = orc.rope_apply(k, grid, table, start_frames).type_as(v)
         n = q.shape[1]
