@@ -58,10 +58,18 @@ def run_config(kernel, rows, heads, window_frames, chunk_frames, iters, warmup, 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush_l2 else None
     res = {"kernel": kernel, "rows": rows, "heads": heads, "window_frames": window_frames,
            "chunk_frames": chunk_frames}
-    if kernel == "append":
+    if kernel in ("append", "append_norm", "append_norm_sliced"):
         table = ops.rope_table_device(build_rope_table(D), dev)
         dst = [min(FRAME_TOKENS, s - n)] * rows
-        fn = lambda: ops.rope_kv_append(q, k, v, kc, vc, table, (chunk_frames, 30, 52), [7] * rows, dst, q_out=out)
+        extra = {}
+        if kernel != "append":          # q/k RMS norm folded in; "_sliced": q, k, v are slices of one q|k|v projection
+            wn = (1 + 0.1 * torch.randn(heads * D, generator=g)).to(torch.bfloat16).to(dev)
+            extra["norm"] = (wn, wn.clone(), 1e-6)
+            if kernel.endswith("sliced"):
+                qkv = torch.stack([q, k, v], dim=2).contiguous()
+                q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        fn = lambda: ops.rope_kv_append(q, k, v, kc, vc, table, (chunk_frames, 30, 52), [7] * rows, dst, q_out=out,
+                                        **extra)
         med, best = _time(fn, iters, warmup, flush)
         nbytes = 6.0 * rows * n * heads * D * 2
         res.update(ms=med, ms_best=best, gbs=nbytes / med / 1e6, bytes_per_launch=nbytes)
@@ -138,7 +146,7 @@ def library_baselines(rows, heads, window_frames, chunk_frames, iters, warmup):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="attn", choices=["append", "attn", "cross"])
+    ap.add_argument("--kernel", default="attn", choices=["append", "append_norm", "append_norm_sliced", "attn", "cross"])
     ap.add_argument("--rows", type=int, default=2)
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--window-frames", type=int, default=21)

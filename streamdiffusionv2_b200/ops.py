@@ -138,30 +138,34 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
         if not can_fuse_norm(q, k, v, wq, wk):
             raise ValueError("this layout cannot take the fused norm: apply rmsnorm first")
         host = step_params is None
-        with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
-            rc = N.lib().sdv2_norm_rope_kv_append(
-                *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
+        # everything is marshalled before the (optionally timed) launch bracket opens
+        args = [*[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
                 f, h, w, N.i64_array(start_frames) if host else None, N.i64_array(dst_begin) if host else None,
                 None if host else step_params.data_ptr(), ge_dev, le_dev, ge_val, le_val,
-                wq.data_ptr(), wk.data_ptr(), float(eps), workspace(q.device).data_ptr(), N.stream_ptr(q.device))
+                wq.data_ptr(), wk.data_ptr(), float(eps), workspace(q.device).data_ptr(), N.stream_ptr(q.device)]
+        fn = N.lib().sdv2_norm_rope_kv_append
+        with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
+            rc = fn(*args)
         N.check(rc, "sdv2_norm_rope_kv_append")
         return q_out
     if step_params is not None:
         if (step_params.dtype != torch.int64 or not step_params.is_contiguous() or step_params.numel() != 4 * B
                 or step_params.device != q.device):
             raise ValueError("step_params must be a contiguous int64 [4, rows] tensor on the same device")
-        with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
-            rc = N.lib().sdv2_rope_kv_append_indirect(
-                *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
+        args = [*[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
                 f, h, w, step_params.data_ptr(), ge_dev, le_dev, N.dtype_code(q.dtype),
-                workspace(q.device).data_ptr(), N.stream_ptr(q.device))
+                workspace(q.device).data_ptr(), N.stream_ptr(q.device)]
+        fn = N.lib().sdv2_rope_kv_append_indirect
+        with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
+            rc = fn(*args)
         N.check(rc, "sdv2_rope_kv_append_indirect")
         return q_out
-    with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
-        rc = N.lib().sdv2_rope_kv_append(
-            *[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
+    args = [*[C.byref(x) for x in views], B, n_new, H, D, k_cache.shape[1], table.data_ptr(), table.shape[0],
             f, h, w, N.i64_array(start_frames), N.i64_array(dst_begin), ge_dev, le_dev, ge_val, le_val,
-            N.dtype_code(q.dtype), workspace(q.device).data_ptr(), N.stream_ptr(q.device))
+            N.dtype_code(q.dtype), workspace(q.device).data_ptr(), N.stream_ptr(q.device)]
+    fn = N.lib().sdv2_rope_kv_append
+    with _Logged("rope_kv_append", 6.0 * B * n_new * H * D * q.element_size()):
+        rc = fn(*args)
     N.check(rc, "sdv2_rope_kv_append")
     return q_out
 
@@ -194,10 +198,11 @@ def attn_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     ws = workspace(q.device)
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
     views = [N.view(t) for t in (q, k_cache, v_cache, out)]
+    args = [*[C.byref(x) for x in views], B, n_q, H, D, k_cache.shape[1], N.i32_array(seq_lens), scale, ws.data_ptr(),
+            ws.numel(), N.stream_ptr(q.device)]
+    fn = N.lib().sdv2_attn_kvcache
     with _Logged("attn_kvcache", 4.0 * n_q * D * H * float(sum(int(x) for x in seq_lens[:B]))):
-        rc = N.lib().sdv2_attn_kvcache(*[C.byref(x) for x in views], B, n_q, H, D, k_cache.shape[1],
-                                       N.i32_array(seq_lens), scale, ws.data_ptr(), ws.numel(),
-                                       N.stream_ptr(q.device))
+        rc = fn(*args)
     N.check(rc, "sdv2_attn_kvcache")
     return out
 
@@ -213,9 +218,11 @@ def cross_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, out: Option
     ws = workspace(q.device)
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
     views = [N.view(t) for t in (q, k, v, out)]
+    args = [*[C.byref(x) for x in views], B, n_q, H, D, k.shape[1], scale, ws.data_ptr(), ws.numel(),
+            N.stream_ptr(q.device)]
+    fn = N.lib().sdv2_cross_attn
     with _Logged("cross_attn", 4.0 * B * n_q * D * H * k.shape[1]):
-        rc = N.lib().sdv2_cross_attn(*[C.byref(x) for x in views], B, n_q, H, D, k.shape[1], scale,
-                                     ws.data_ptr(), ws.numel(), N.stream_ptr(q.device))
+        rc = fn(*args)
     N.check(rc, "sdv2_cross_attn")
     return out
 

@@ -21,7 +21,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from .ring_state import RingState
-from .stage_transport import StageLink, StagePacket, contiguous_block_ranges
+from .stage_transport import StageLink, StagePacket, contiguous_block_ranges, partition_by_cost
 from .stream_pipeline import StreamPipeline, assign_ints
 
 
@@ -35,15 +35,22 @@ class StreamRestart(Exception):
 
 class PipelineStageRunner:
     def __init__(self, pipe: StreamPipeline, link: StageLink, rank: int, world_size: int,
-                 block_ranges: Optional[Sequence[Sequence[int]]] = None, prefetch: bool = False):
+                 block_ranges: Optional[Sequence[Sequence[int]]] = None, prefetch: bool = False,
+                 half_ranges: Optional[Sequence[Sequence[int]]] = None):
         # prefetch: post the next receive one chunk ahead.  Off by default: a posted NCCL receive is a
         # kernel that spins on a few SMs until its data arrives, and the attention CTAs (which need a
         # whole SM's shared memory) cannot run on those SMs meanwhile; a 20 MB hop takes ~30 us anyway.
         self.prefetch = prefetch
         self.pipe, self.link, self.rank, self.world = pipe, link, rank, world_size
-        ranges = block_ranges or contiguous_block_ranges(pipe.num_transformer_blocks, world_size)
-        self.block_ranges = [[int(a), int(b)] for a, b in ranges]     # of every stage
-        self.block_range = list(self.block_ranges[rank])
+        # Stage ranges are kept in half-block units (half 2i = self-attention part of block i, half
+        # 2i + 1 = the rest of it): the reference splits at whole blocks (inference_pipe.py:59-74), which
+        # is what `block_ranges` gives; `half_ranges` lets two stages meet inside a block.
+        if half_ranges is None:
+            ranges = block_ranges or contiguous_block_ranges(pipe.num_transformer_blocks, world_size)
+            half_ranges = [[2 * int(a), 2 * int(b)] for a, b in ranges]
+        self._set_ranges(half_ranges)
+        self._measure_left = 0    # steps still to run with every half block timed (measure_costs)
+        self._measured: List[list] = []
         self.role = "input" if rank == 0 else ("output" if rank == world_size - 1 else "middle")
         self.items = 0            # chunks processed (stage 0: sent)
         self.received = 0         # stage 0: packets taken from the closing edge
@@ -51,9 +58,96 @@ class PipelineStageRunner:
         self.stage_events = None  # set to [] to record (start, end) CUDA events around each stage compute
         self._quiet = True        # nothing in flight on the links: a step may synchronise the device (graph recording)
 
+    def _set_ranges(self, half_ranges: Sequence[Sequence[int]]) -> None:
+        total = 2 * self.pipe.num_transformer_blocks
+        hr = [[int(a), int(b)] for a, b in half_ranges]
+        if (len(hr) != self.world or hr[0][0] != 0 or hr[-1][1] != total
+                or any(a[1] != b[0] for a, b in zip(hr, hr[1:])) or any(b <= a for a, b in hr)):
+            raise ValueError("stage ranges must be contiguous, non-empty and cover every block")
+        self.half_ranges = hr
+        self.half_range = list(hr[self.rank])
+        # blocks whose self-attention (and therefore K/V cache) lives on each stage
+        self.block_ranges = [[(a + 1) // 2, (b + 1) // 2] for a, b in hr]
+        self.block_range = list(self.block_ranges[self.rank])
+        self._whole_blocks = all(a % 2 == 0 and b % 2 == 0 for a, b in hr)
+
     @property
     def owned_blocks(self) -> range:
         return range(self.block_range[0], self.block_range[1])
+
+    def _range_args(self) -> dict:
+        """How this stage's range is handed to the pipeline: as whole blocks where it can be."""
+        if self._whole_blocks:
+            return {"block_num": [self.half_range[0] // 2, self.half_range[1] // 2]}
+        return {"block_num": self.block_range, "half_blocks": self.half_range}
+
+    # ------------------------------------------------------------------ measured stage costs
+    def measure_costs(self, steps: int = 3) -> None:
+        """Have the next `steps` chunk steps of this rank run launch by launch (no graph replay) with
+        every half block and the whole stage timed; `plan_ranges` then uses the medians.  Call on every
+        rank before the same chunk."""
+        self._measure_left, self._measured = int(steps), []
+
+    def _measured_step(self, run):
+        """Run one stage computation, timed per half block when a measurement is in progress."""
+        if self._measure_left <= 0:
+            return run()
+        from .wan_model import _stamp
+        model, pipe = self.pipe.generator.model, self.pipe
+        graphs, pipe.step_graphs = pipe.step_graphs, None
+        model.half_stamps = []
+        t0 = _stamp(pipe.hidden_states)
+        try:
+            out = run()
+        finally:
+            t1 = _stamp(pipe.hidden_states)
+            self._measured.append((model.half_stamps, t0, t1))
+            model.half_stamps = None
+            pipe.step_graphs = graphs
+            self._measure_left -= 1
+        return out
+
+    def plan_ranges(self, granularity: str = "half") -> List[List[int]]:
+        """New stage ranges (half-block units) from the measured costs: every rank contributes the
+        median time of each half block it ran and its stage's extra time (everything that is not a
+        block: embedding, row shift, head, x0 conversion, re-noising), one all-gather on the default
+        process group, then the same exact partition on every rank (`partition_by_cost`).
+        granularity "block" keeps the boundaries at whole blocks.  Collective: call on every rank."""
+        import statistics
+        import torch.distributed as dist
+        if not self._measured or self._measure_left > 0:
+            raise RuntimeError("measure_costs() and the measured steps come first")
+        n_half = 2 * self.pipe.num_transformer_blocks
+        dev = self.pipe.device
+        if dev.type == "cuda":
+            torch.cuda.synchronize(dev)
+
+        def span(a, b):
+            return a.elapsed_time(b) if hasattr(a, "elapsed_time") else (b - a) * 1e3
+
+        per_half: dict = {}
+        extras = []
+        for stamps, t0, t1 in self._measured:
+            inside = 0.0
+            for h, a, b in stamps:
+                d = span(a, b)
+                per_half.setdefault(h, []).append(d)
+                inside += d
+            extras.append(span(t0, t1) - inside)
+        mine = torch.zeros(n_half + 1, dtype=torch.float64)
+        for h, v in per_half.items():
+            mine[h] = statistics.median(v)
+        mine[n_half] = max(statistics.median(extras), 0.0)
+        mine = mine.to(dev)
+        every = [torch.zeros_like(mine) for _ in range(self.world)]
+        dist.all_gather(every, mine)
+        every = [t.cpu() for t in every]
+        costs = torch.stack([t[:n_half] for t in every]).max(dim=0).values.tolist()   # one rank measured each half
+        overheads = [float(t[n_half]) for t in every]
+        if min(costs) <= 0.0:
+            raise RuntimeError("a half block was not measured on any rank")
+        self.last_costs = {"per_half_ms": costs, "stage_extra_ms": overheads}
+        return partition_by_cost(costs, overheads, boundary_step=2 if granularity == "block" else 1)
 
     # ------------------------------------------------------------------ one chunk on this rank
     def step(self, chunk_idx: int = 0, noise: Optional[torch.Tensor] = None, current_start: Optional[int] = None,
@@ -81,9 +175,9 @@ class PipelineStageRunner:
             elif self.prefetch and self.items == self.world - 1 and not last:
                 link.post_recv()
             ev = self._mark()
-            act, _ = pipe.inference(noise=noise, current_start=current_start, current_end=current_end,
-                                    current_step=current_step, block_mode="input", block_num=self.block_range,
-                                    allow_record=self._quiet)
+            act, _ = self._measured_step(lambda: pipe.inference(
+                noise=noise, current_start=current_start, current_end=current_end, current_step=current_step,
+                block_mode="input", allow_record=self._quiet, **self._range_args()))
             self._quiet = False
             self._mark(ev)
             link.send(chunk_idx, act, pipe.hidden_states, pipe.generator.model.last_patched_x_shape,
@@ -105,10 +199,10 @@ class PipelineStageRunner:
             link.post_recv()
         step = None if pkt.current_step < 0 else pkt.current_step
         ev = self._mark()
-        out, pshape = pipe.inference(noise=pkt.latents, current_start=pkt.starts, current_end=pkt.ends,
-                                     current_step=step, block_mode=self.role, block_num=self.block_range,
-                                     patched_x_shape=pkt.patched_x_shape, block_x=pkt.activations,
-                                     starts_host=pkt.starts, allow_record=self._quiet)
+        out, pshape = self._measured_step(lambda: pipe.inference(
+            noise=pkt.latents, current_start=pkt.starts, current_end=pkt.ends, current_step=step, block_mode=self.role,
+            patched_x_shape=pkt.patched_x_shape, block_x=pkt.activations, starts_host=pkt.starts,
+            allow_record=self._quiet, **self._range_args()))
         self._quiet = False
         self._mark(ev)
         if self.role == "middle":
@@ -160,9 +254,9 @@ class PipelineStageRunner:
     # ------------------------------------------------------------------ moving blocks between stages
     _QUEUE_SLOTS = 64   # evict-queue entries shipped per row (a queue holds at most one entry per cache frame)
 
-    def rebalance(self, new_ranges: Sequence[Sequence[int]]) -> None:
-        """Switch to new contiguous block ranges and move the K/V state of every block whose owner
-        changes (streamv2v/inference_pipe.py:802-843, communication/kv_cache_manager.py:48-144).
+    def rebalance(self, new_ranges: Sequence[Sequence[int]], halves: bool = False) -> None:
+        """Switch to new contiguous stage ranges (whole blocks, or half-block units with `halves`)
+        and move the K/V state of every block whose self-attention changes owner (streamv2v/inference_pipe.py:802-843, communication/kv_cache_manager.py:48-144).
         Call on every rank with the same ranges, directly after `quiesce()`: with the ring empty all
         stages have processed the same chunks, so the state moves as it is - K, V, both index
         tensors, the step counters and the block's evict queue (which the reference leaves behind).
@@ -170,12 +264,13 @@ class PipelineStageRunner:
         import torch.distributed as dist
         if not self._quiet:
             raise RuntimeError("rebalance() needs an empty ring: call quiesce() first")
-        new_ranges = [[int(a), int(b)] for a, b in new_ranges]
+        new_half = [[int(a) * (1 if halves else 2), int(b) * (1 if halves else 2)] for a, b in new_ranges]
         total = self.pipe.num_transformer_blocks
-        if (len(new_ranges) != self.world or new_ranges[0][0] != 0 or new_ranges[-1][1] != total
-                or any(a[1] != b[0] for a, b in zip(new_ranges, new_ranges[1:]))
-                or any(b <= a for a, b in new_ranges)):
+        if (len(new_half) != self.world or new_half[0][0] != 0 or new_half[-1][1] != 2 * total
+                or any(a[1] != b[0] for a, b in zip(new_half, new_half[1:]))
+                or any(b <= a for a, b in new_half)):
             raise ValueError("block ranges must be contiguous, non-empty and cover every block")
+        new_ranges = [[(a + 1) // 2, (b + 1) // 2] for a, b in new_half]   # owners of the self-attention halves
 
         def owners(ranges):
             out = [0] * total
@@ -231,8 +326,7 @@ class PipelineStageRunner:
                     if m[base] >= 0:
                         queues.append([int(x) for x in m[base + 1:base + 1 + m[base]]])
                 module.evict_idx = queues if queues else None
-        self.block_ranges = new_ranges
-        self.block_range = list(new_ranges[self.rank])
+        self._set_ranges(new_half)
         if pipe.step_graphs is not None:
             pipe.step_graphs.forget()
 

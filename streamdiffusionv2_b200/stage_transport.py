@@ -85,6 +85,44 @@ def balanced_block_ranges(total_blocks: int, world_size: int) -> List[List[int]]
     return out
 
 
+def partition_by_cost(costs: Sequence[float], overheads: Sequence[float], boundary_step: int = 1) -> List[List[int]]:
+    """Contiguous, non-empty ranges of `costs` (one per stage, in order) that minimise the slowest
+    stage's time max_r(overheads[r] + sum of the costs in range r): the run-time counterpart of the
+    reference's compute_balanced_split (streamv2v/communication/utils.py:141-229), which moves
+    whole blocks proportionally to the measured imbalance; this one takes the measured cost of
+    every unit and the fixed extra time of every stage (patch embedding and row shift on the
+    first, head and re-noising on the last) and solves the partition exactly.  `boundary_step` = 2
+    with costs per half block restricts the boundaries to whole blocks.  Ties keep earlier stages
+    shorter.  Returns [[start, end), ...] in units of `costs`."""
+    n, w = len(costs), len(overheads)
+    if w < 1 or n < w * boundary_step:
+        raise ValueError("fewer units than stages")
+    prefix = [0.0]
+    for c in costs:
+        prefix.append(prefix[-1] + float(c))
+    cuts = list(range(0, n + 1, boundary_step))
+    if cuts[-1] != n:
+        raise ValueError("the number of units is not a multiple of boundary_step")
+    inf = float("inf")
+    # best[r][j]: smallest possible slowest-stage time for stages 0..r covering units [0, cuts[j])
+    best = [[inf] * len(cuts) for _ in range(w)]
+    back = [[-1] * len(cuts) for _ in range(w)]
+    for j in range(1, len(cuts)):
+        best[0][j] = overheads[0] + prefix[cuts[j]]
+    for r in range(1, w):
+        for j in range(r + 1, len(cuts)):
+            for i in range(r, j):
+                t = max(best[r - 1][i], overheads[r] + prefix[cuts[j]] - prefix[cuts[i]])
+                if t < best[r][j]:
+                    best[r][j], back[r][j] = t, i
+    out, j = [], len(cuts) - 1
+    for r in range(w - 1, -1, -1):
+        i = back[r][j] if r > 0 else 0
+        out.append([cuts[i], cuts[j]])
+        j = i
+    return out[::-1]
+
+
 class _Edge:
     """One direction of one ring edge as seen from this rank."""
 

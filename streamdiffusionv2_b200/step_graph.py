@@ -62,8 +62,9 @@ def _cache_pointers(layers: Sequence[tuple]) -> List[int]:
     out: List[int] = []
     for entry in layers:
         kv = entry[1]
-        out += [kv["k"].data_ptr(), kv["v"].data_ptr(), kv["global_end_index"].data_ptr(),
-                kv["local_end_index"].data_ptr()]
+        if kv is not None:            # None: a block of which only the cross-attention half runs here
+            out += [kv["k"].data_ptr(), kv["v"].data_ptr(), kv["global_end_index"].data_ptr(),
+                    kv["local_end_index"].data_ptr()]
         if len(entry) > 2 and entry[2] is not None and entry[2].get("is_init"):
             out += [entry[2]["k"].data_ptr(), entry[2]["v"].data_ptr()]
     return out
@@ -100,6 +101,8 @@ class StepGraphs:
             module, kv = entry[0], entry[1]
             if len(entry) > 2 and entry[2] is not None and not entry[2].get("is_init", False):
                 return False
+            if kv is None:
+                continue
             if module.sink_size > 0 and module.adapt_sink_thr > -1:
                 return False
             st = RingState.of(kv)

@@ -84,24 +84,25 @@ class DiffusionWrapper(nn.Module):
 
     def forward_input(self, noisy_image_or_video, conditional_dict, timestep, block_mode="input", block_num=None,
                       kv_cache=None, crossattn_cache=None, current_start=None, current_end=None,
-                      patched_x_shape=None, block_x=None):
+                      patched_x_shape=None, block_x=None, half_blocks=None):
         """First or middle pipeline stage: returns (activations [B, L, dim], patched_x_shape)."""
         assert kv_cache is not None, "kv_cache must be provided"
         x = block_x if (block_x is not None and block_mode == "middle") else noisy_image_or_video.permute(0, 2, 1, 3, 4)
         return self.model(x, t=timestep, context=conditional_dict["prompt_embeds"], seq_len=self.seq_len,
                           kv_cache=kv_cache, crossattn_cache=crossattn_cache, current_start=current_start,
                           current_end=current_end, block_mode=block_mode, block_num=block_num,
-                          patched_x_shape=patched_x_shape)
+                          patched_x_shape=patched_x_shape, **({} if half_blocks is None else {"half_blocks": half_blocks}))
 
     def forward_output(self, noisy_image_or_video, conditional_dict, timestep, block_mode="output", block_num=None,
                        kv_cache=None, crossattn_cache=None, current_start=None, current_end=None,
-                       patched_x_shape=None, block_x=None):
+                       patched_x_shape=None, block_x=None, half_blocks=None):
         """Last pipeline stage: remaining blocks, head, x0 of the stage's latents."""
         assert kv_cache is not None, "kv_cache must be provided"
         flow = self.model(block_x, t=timestep, context=conditional_dict["prompt_embeds"], seq_len=self.seq_len,
                           kv_cache=kv_cache, crossattn_cache=crossattn_cache, current_start=current_start,
                           current_end=current_end, block_mode=block_mode, block_num=block_num,
-                          patched_x_shape=patched_x_shape).permute(0, 2, 1, 3, 4)
+                          patched_x_shape=patched_x_shape,
+                          **({} if half_blocks is None else {"half_blocks": half_blocks})).permute(0, 2, 1, 3, 4)
         return self._x0(flow.flatten(0, 1), noisy_image_or_video.flatten(0, 1),
                         timestep.flatten(0, 1)).unflatten(0, flow.shape[:2])
 
@@ -162,12 +163,16 @@ class StreamPipeline(nn.Module):
         self.step_graphs = StepGraphs(self.device, self.num_transformer_blocks, self.hidden_states.shape[0])
         self._graph_in = torch.empty_like(self.hidden_states)
 
-    def _forward(self, key, fn, blocks: range, allow_record: bool = True):
-        """fn() eagerly, or through the step graphs when they are enabled."""
+    def _forward(self, key, fn, blocks: range, allow_record: bool = True, cross_blocks: Optional[range] = None):
+        """fn() eagerly, or through the step graphs when they are enabled.  `blocks`: the blocks whose
+        self-attention (K/V cache) runs in fn; `cross_blocks`: those whose cross-attention does (the
+        same unless a stage boundary lies inside a block)."""
         if self.step_graphs is None:
             return fn(), False
-        layers = [(self.generator.model.blocks[i].self_attn, self.kv_cache1[i], self.crossattn_cache[i])
-                  for i in blocks]
+        cross = blocks if cross_blocks is None else cross_blocks
+        layers = [(self.generator.model.blocks[i].self_attn, self.kv_cache1[i],
+                   self.crossattn_cache[i] if i in cross else None) for i in blocks]
+        layers += [(None, None, self.crossattn_cache[i]) for i in cross if i not in blocks]
         n_new = self.hidden_states.shape[1] * self.frame_seq_length
         before = self.step_graphs.replays
         out = self.step_graphs.run(key, fn, layers, self._starts_host, n_new, allow_record=allow_record)
@@ -336,10 +341,11 @@ class StreamPipeline(nn.Module):
 
     def inference(self, noise, current_start, current_end, current_step, block_mode="input", block_num=None,
                   patched_x_shape=None, block_x=None, starts_host: Optional[Sequence[int]] = None,
-                  allow_record: bool = True):
+                  allow_record: bool = True, half_blocks: Optional[Sequence[int]] = None):
         """One chunk step of one pipeline stage (causal_stream_inference.py:350-420).  'input':
         shift the new chunk in and run the first block range; 'middle'/'output': adopt the
-        previous stage's activations, latents and row starts, run this stage's range."""
+        previous stage's activations, latents and row starts, run this stage's range.  `half_blocks`
+        = (a, b) gives the range in half-block units instead of `block_num` (see the model)."""
         if block_mode == "input":
             self._shift_in(noise, current_start, current_end)
         else:
@@ -367,12 +373,17 @@ class StreamPipeline(nn.Module):
                       current_end=self.kv_cache_ends, block_mode=block_mode, block_num=block_num,
                       patched_x_shape=patched_x_shape, block_x=self.block_x)
         rng = [int(i) for i in (block_num.tolist() if isinstance(block_num, torch.Tensor) else block_num)]
-        owned = range(rng[0], rng[-1])
+        owned, cross = range(rng[0], rng[-1]), None
+        if half_blocks is not None:
+            lo, hi = int(half_blocks[0]), int(half_blocks[1])
+            common["half_blocks"] = (lo, hi)
+            owned, cross = range((lo + 1) // 2, (hi + 1) // 2), range(lo // 2, hi // 2)
+            rng = [lo / 2, hi / 2]
         key = (block_mode, rng[0], rng[-1], tuple(self.hidden_states.shape),
                tuple(int(i) for i in patched_x_shape) if isinstance(patched_x_shape, (list, tuple)) else None)
         if block_mode == "output":
             fn = lambda: self.generator.forward_output(noisy_image_or_video=self.hidden_states, **common)
-            denoised, replayed = self._forward(key, fn, owned, allow_record)
+            denoised, replayed = self._forward(key, fn, owned, allow_record, cross)
             return self._renoise(denoised.clone() if replayed else denoised), None
         fn = lambda: self.generator.forward_input(noisy_image_or_video=self.hidden_states, **common)
-        return self._forward(key, fn, owned, allow_record)[0]
+        return self._forward(key, fn, owned, allow_record, cross)[0]

@@ -118,8 +118,11 @@ class DiTBlock(nn.Module):
         self.ffn = nn.Sequential(nn.Linear(dim, ffn_dim), nn.GELU(approximate="tanh"), nn.Linear(ffn_dim, dim))
         self.modulation = nn.Parameter(torch.randn(1, 6, dim) / dim ** 0.5)
 
-    def forward(self, x, e, grid_sizes, freqs, context, kv_cache, crossattn_cache, current_start):
-        """x [B, L, C]; e [B, F, 6, C] (per-frame modulation from the timestep embedding)."""
+    def forward(self, x, e, grid_sizes, freqs, context, kv_cache, crossattn_cache, current_start, part="all"):
+        """x [B, L, C]; e [B, F, 6, C] (per-frame modulation from the timestep embedding).
+        `part` runs the block in two halves for pipeline stages that meet inside a block: "attn" ends
+        after the self-attention residual (causal_model.py:463-471), "rest" resumes there (cross-
+        attention and FFN, :473-483); "attn" then "rest" computes exactly what "all" does."""
         frames = e.shape[1]
         per_frame = x.shape[1] // frames
         shift_a, scale_a, gate_a, shift_f, scale_f, gate_f = (self.modulation.unsqueeze(1) + e).chunk(6, dim=2)
@@ -136,9 +139,12 @@ class DiTBlock(nn.Module):
                 return ops.gate_residual(x, y, gate, frames)
             return x + (y.unflatten(1, (frames, per_frame)) * gate).flatten(1, 2)
 
-        y = self.self_attn(norm_modulate(self.norm1, x, scale_a, shift_a), None, grid_sizes, freqs, None,
-                           kv_cache, current_start, None)
-        x = add_gated(x, y, gate_a)
+        if part != "rest":
+            y = self.self_attn(norm_modulate(self.norm1, x, scale_a, shift_a), None, grid_sizes, freqs, None,
+                               kv_cache, current_start, None)
+            x = add_gated(x, y, gate_a)
+            if part == "attn":
+                return x
         x = x + self.cross_attn(self.norm3(x), context, None, crossattn_cache=crossattn_cache)
         y = self.ffn(norm_modulate(self.norm2, x, scale_f, shift_f))
         return add_gated(x, y, gate_f)
@@ -156,6 +162,16 @@ class OutputHead(nn.Module):
         frames = e.shape[1]
         shift, scale = (self.modulation.unsqueeze(1) + e).chunk(2, dim=2)
         return self.head(self.norm(x).unflatten(1, (frames, x.shape[1] // frames)) * (1 + scale) + shift)
+
+
+def _stamp(x: torch.Tensor):
+    """A point in time on x's device: a recorded CUDA event, or host seconds for CPU tensors."""
+    if x.is_cuda:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+    import time
+    return time.perf_counter()
 
 
 def _as_ints(v) -> List[int]:
@@ -193,6 +209,9 @@ class CausalWanModel(nn.Module):
         # plain attribute, not a buffer: .to(dtype) must not touch it (causal_model.py:630-638)
         self.freqs = build_rope_table(head_dim)
         self.num_frame_per_block = 1
+        # set to a list to have every half block of a forward timed on its own: (half index, start, end)
+        # stamps (CUDA events on a GPU, seconds on the host) are appended; None = off
+        self.half_stamps = None
         self.last_patched_x_shape = None
         self._shape_tensors = {}
         self.reset_parameters()
@@ -220,11 +239,14 @@ class CausalWanModel(nn.Module):
 
     def _forward_inference(self, x, t, context, seq_len, clip_fea=None, y=None, kv_cache=None, crossattn_cache=None,
                            current_start=0, current_end=0, block_mode="input", block_num=(-1,),
-                           patched_x_shape=None):
+                           patched_x_shape=None, half_blocks=None):
         """x: [B, C, F, H, W] latents ('input' mode) or [B, L, dim] activations of the previous
         pipeline stage ('middle' / 'output'); t: [B, F] timesteps; context: [B, Lt, text_dim].
         Returns [B, C, F, H, W], or (activations, patched_x_shape) when the stage ends before the
-        last block.  block_num = (first_block, end_block) of this stage."""
+        last block.  block_num = (first_block, end_block) of this stage.  `half_blocks` = (a, b), when
+        given, replaces it with a range in half-block units (half 2i = self-attention part of block i,
+        half 2i + 1 = its cross-attention + FFN part), so that stages may meet inside a block; the
+        reference knows whole blocks only (causal_model.py:794-833)."""
         device = self.patch_embedding.weight.device
         if self.freqs.device != device:
             self.freqs = self.freqs.to(device)
@@ -252,12 +274,27 @@ class CausalWanModel(nn.Module):
         e = self.time_embedding(timestep_features(self.freq_dim, t.flatten()).type_as(x))
         e0 = self.time_projection(e).unflatten(1, (6, self.dim)).unflatten(0, t.shape)
 
+        n_blocks = len(self.blocks)
+        if half_blocks is not None:
+            lo, hi = int(half_blocks[0]), int(half_blocks[1])
+            if not 0 <= lo <= hi <= 2 * n_blocks:
+                raise ValueError("half_blocks outside the model")
+            bounded = True
+        else:
+            lo = 2 * first if block_mode in ("output", "middle") else 0
+            bounded = block_mode in ("input", "middle") and 0 <= last <= n_blocks
+            hi = 2 * last if bounded else 2 * n_blocks
+        if block_mode == "output":
+            hi = 2 * n_blocks
+        # a first or middle stage hands activations on; a range that reaches the end of the model does so
+        # only in 'input' mode (the reference's convention, causal_model.py:819-833)
+        hands_on = block_mode in ("input", "middle") and bounded and (hi < 2 * n_blocks or block_mode == "input")
+
         # the text embedding only feeds the cross-attention K/V projections, which are skipped once a
         # block's crossattn_cache is initialised: do not recompute it for blocks that will not read it
-        lo_blk = first if block_mode in ("output", "middle") else 0
-        hi_blk = last if block_mode in ("input", "middle") and 0 <= last <= len(self.blocks) else len(self.blocks)
+        # (a block reads it in its second half)
         need_ctx = crossattn_cache is None or any(
-            c is None or not c.get("is_init", False) for c in crossattn_cache[lo_blk:hi_blk])
+            c is None or not c.get("is_init", False) for c in crossattn_cache[lo // 2:hi // 2])
         ctx = None
         if need_ctx:
             ctx = context if isinstance(context, torch.Tensor) else torch.stack(
@@ -269,13 +306,26 @@ class CausalWanModel(nn.Module):
         starts = CA.HostStarts(current_start, CA.host_starts(current_start, bsz)) \
             if isinstance(current_start, torch.Tensor) else current_start
 
-        for idx, block in enumerate(self.blocks):
-            if block_mode in ("output", "middle") and idx < first:
-                continue
-            if block_mode in ("input", "middle") and idx == last:
-                return x, patched_x_shape
-            x = block(x, e0, grid_sizes, self.freqs, ctx, kv_cache[idx], crossattn_cache[idx], starts)
-        if block_mode == "input" and last == len(self.blocks):
+        stamps = self.half_stamps
+        h = lo
+        while h < hi:
+            idx, second = divmod(h, 2)
+            if second:
+                part, step = "rest", 1
+            elif h + 1 < hi and stamps is None:
+                part, step = "all", 2
+            else:
+                part, step = "attn", 1
+            t0 = _stamp(x) if stamps is not None else None
+            block = self.blocks[idx]
+            if part == "all":
+                x = block(x, e0, grid_sizes, self.freqs, ctx, kv_cache[idx], crossattn_cache[idx], starts)
+            else:
+                x = block(x, e0, grid_sizes, self.freqs, ctx, kv_cache[idx], crossattn_cache[idx], starts, part=part)
+            if stamps is not None:
+                stamps.append((h, t0, _stamp(x)))
+            h += step
+        if hands_on:
             return x, patched_x_shape
 
         x = self.head(x, e.unflatten(0, t.shape).unsqueeze(2))

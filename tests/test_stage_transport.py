@@ -41,7 +41,7 @@ class _Patch:
         setattr(obj, name, value)
 
 
-def _worker_pipeline(rank, world, port, ranges, quiesce_every, q, park_at=()):
+def _worker_pipeline(rank, world, port, ranges, quiesce_every, q, park_at=(), halves=False, replan_at=None):
     try:
         _init(rank, world, port)
         import fake_ops
@@ -61,15 +61,28 @@ def _worker_pipeline(rank, world, port, ranges, quiesce_every, q, park_at=()):
             rows = len(case["levels"])
             link = StageLink(rank, world, torch.device("cpu"), (rows, fs * case["frames"], cases.MODEL_KW["dim"]),
                              tuple(pipe.hidden_states.shape), dtype=torch.float32, timeout_s=60)
-            runner = PipelineStageRunner(pipe, link, rank, world, ranges)
-            outs, states = [], []
+            runner = (PipelineStageRunner(pipe, link, rank, world, half_ranges=ranges) if halves
+                      else PipelineStageRunner(pipe, link, rank, world, ranges))
+            outs, states, planned = [], [], None
             for i, (noise, (cs, ce)) in enumerate(zip(chunks, sched)):
                 last = quiesce_every > 0 and i % quiesce_every == quiesce_every - 1
+                if replan_at is not None and i == replan_at[0]:
+                    runner.measure_costs(replan_at[1] - replan_at[0])
+                if replan_at is not None and i == replan_at[1] - 1:
+                    last = True
+                if replan_at is not None and i == replan_at[1]:
+                    # measured steps are over and the ring was emptied: plan from the gathered costs and move
+                    planned = runner.plan_ranges(replan_at[2])
+                    runner.rebalance(planned, halves=True)
                 o = runner.step(i, noise, cs, ce, None, last=last)
                 if o is not None:
                     outs.append(o.clone().numpy())
                 if last:
                     runner.quiesce()       # ring emptied mid-stream; results must not change
+                if planned is not None and i == replan_at[1]:
+                    states.append({"planned": planned, "half_range": runner.half_range,
+                                   "costs": runner.last_costs})
+                    continue
                 if i + rank in park_at:    # rank r is r chunks behind rank 0: the ring stays full
                     runner.park()
                     dist.barrier()
@@ -367,3 +380,80 @@ def test_block_ranges_follow_the_reference_split():
     for n, w in ((30, 4), (30, 8), (40, 4), (7, 3)):
         rr = r(n, w)
         assert rr[0][0] == 0 and rr[-1][1] == n and all(rr[i][1] == rr[i + 1][0] for i in range(w - 1))
+
+
+# ---------------------------------------------------------------------------------------------
+# stage boundaries inside a block, and ranges planned from measured costs
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("world,half_ranges", [
+    (2, [[0, 3], [3, 6]]),            # stage A: block 0 and the self-attention of block 1
+    (2, [[0, 1], [1, 6]]),            # stage A: only the self-attention of block 0
+    (3, [[0, 3], [3, 4], [4, 6]]),    # a middle stage that runs only the second half of block 1
+])
+def test_half_block_stage_boundaries_reproduce_the_reference_fixture(world, half_ranges):
+    """Stages may meet after a block's self-attention residual; the stream is the one the reference's
+    whole-block pipeline produced."""
+    case = cases.MODEL_CASES["m_stages"]
+    _, z = cases.load_fixture("m_stages")
+    res = _run(_worker_pipeline, world, half_ranges, 0, {"halves": True})
+    for r, v in res.items():
+        assert v[0] == "ok", v[1]
+    outs = res[world - 1][1]
+    assert len(outs) == case["chunks"]
+    if world == 2:                      # the fixture is a two-stage run (ring depth 2)
+        for i, o in enumerate(outs):
+            assert np.abs(o - z[f"out_{i}"]).max() < 5e-4, i
+    else:                               # three stages: the deeper ring delays the re-noised rows; compare with whole blocks
+        plain = _run(_worker_pipeline, 3, [[0, 1], [1, 2], [2, 3]], 0)
+        for a, b in zip(outs, plain[2][1]):
+            assert np.abs(a - b).max() < 1e-5
+
+
+def test_partition_by_cost_is_optimal_and_respects_block_boundaries():
+    import itertools
+    from streamdiffusionv2_b200.stage_transport import partition_by_cost
+    g = torch.Generator().manual_seed(5)
+    for n, w in ((6, 2), (8, 3), (10, 4), (12, 3)):
+        costs = (0.2 + torch.rand(n, generator=g)).tolist()
+        over = (0.5 * torch.rand(w, generator=g)).tolist()
+        for step in (1, 2):
+            got = partition_by_cost(costs, over, boundary_step=step)
+            assert got[0][0] == 0 and got[-1][1] == n and all(a[1] == b[0] for a, b in zip(got, got[1:]))
+            assert all(b > a and a % step == 0 and b % step == 0 for a, b in got)
+            t_got = max(over[r] + sum(costs[a:b]) for r, (a, b) in enumerate(got))
+            best = min(max(over[r] + sum(costs[a:b]) for r, (a, b) in enumerate(zip((0,) + cut, cut + (n,))))
+                       for cut in itertools.combinations(range(step, n, step), w - 1))
+            assert abs(t_got - best) < 1e-12, (n, w, step)
+    # 30 equal blocks on 8 stages, extra work on the first and the last stage: the remainder moves off the
+    # ends (3-4-4-4-4-4-4-3); half-block boundaries cannot beat that here (any 8 consecutive halves are 4 blocks'
+    # worth and the average stage holds 7.5), but they do where the counts leave room
+    t = lambda rs, c, o: max(o[r] + sum(c[a:b]) for r, (a, b) in enumerate(rs))
+    halves, over = [1.4, 0.45] * 30, [0.45, 0, 0, 0, 0, 0, 0, 0.25]
+    whole = partition_by_cost(halves, over, boundary_step=2)
+    assert [(b - a) // 2 for a, b in whole] == [3, 4, 4, 4, 4, 4, 4, 3]
+    assert t(whole, halves, over) == pytest.approx(4 * 1.85)
+    assert t(partition_by_cost(halves, over), halves, over) <= t(whole, halves, over) + 1e-12
+    three = [1.0, 1.0] * 3
+    assert t(partition_by_cost(three, [0, 0], 2), three, [0, 0]) == pytest.approx(4.0)
+    assert t(partition_by_cost(three, [0, 0], 1), three, [0, 0]) == pytest.approx(3.0)
+    with pytest.raises(ValueError):
+        partition_by_cost([1.0], [0.0, 0.0])
+
+
+def test_measured_costs_give_every_rank_the_same_plan_and_the_stream_survives_the_move():
+    """Three measured steps, one all-gather, the exact partition on every rank, blocks (or halves of
+    blocks) moved with their K/V state mid-stream: the outputs stay those of the fixture."""
+    case = cases.MODEL_CASES["m_stages"]
+    _, z = cases.load_fixture("m_stages")
+    nblk, split = cases.MODEL_KW["num_layers"], case["split"]
+    res = _run(_worker_pipeline, 2, [[0, split], [split, nblk]], 0, {"replan_at": (1, 4, "half")})
+    for r, v in res.items():
+        assert v[0] == "ok", v[1]
+    info = [next(s for s in res[r][2] if "planned" in s) for r in (0, 1)]
+    assert info[0]["planned"] == info[1]["planned"]                       # same plan everywhere
+    assert info[0]["half_range"] == info[0]["planned"][0] and info[1]["half_range"] == info[1]["planned"][1]
+    assert len(info[0]["costs"]["per_half_ms"]) == 2 * nblk and min(info[0]["costs"]["per_half_ms"]) > 0
+    outs = res[1][1]
+    assert len(outs) == case["chunks"]
+    for i, o in enumerate(outs):
+        assert np.abs(o - z[f"out_{i}"]).max() < 5e-4, i
