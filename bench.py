@@ -668,8 +668,10 @@ def run_pipeline(args):
     dist.init_process_group("nccl")   # lazy communicators: the stage links create theirs one edge at a time
     peaks = measured_peaks()
     pipe = build_pipeline(device)
+    # "measured" starts on the reference's split and re-plans from measured costs once the caches are full
     split = balanced_block_ranges if args.block_split == "balanced" else contiguous_block_ranges
     ranges = split(MODEL_1P3B["num_layers"], world)
+    measured = args.block_split.startswith("measured")
     role = "input" if rank == 0 else ("output" if rank == world - 1 else "middle")
     g = torch.Generator(device="cpu").manual_seed(2)
     h, w = LATENT_HW
@@ -738,6 +740,30 @@ def run_pipeline(args):
             t = torch.tensor(values, dtype=torch.float64, device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return t.tolist()
+
+        reference_split = None
+        if measured:
+            # one region on the reference's split (kept in the record), then three launch-by-launch steps
+            # with every half block timed, one all-gather, the exact partition, blocks moved with their K/V
+            runner.stage_events = []
+            ref_ms = max_over_ranks([region(resident)])[0]
+            ref_stage = statistics.mean(a.elapsed_time(b) for a, b in runner.stage_events)
+            per_stage = [torch.zeros(1, dtype=torch.float64, device=device) for _ in range(world)]
+            dist.all_gather(per_stage, torch.tensor([ref_stage], dtype=torch.float64, device=device))
+            reference_split = {"stage_blocks": [list(r) for r in runner.block_ranges],
+                               "value": VIDEO_FRAMES_PER_CHUNK * args.steps / (ref_ms / 1e3),
+                               "ms_per_step": ref_ms / args.steps,
+                               "stage_compute_ms": [round(t.item(), 3) for t in per_stage]}
+            runner.stage_events = None
+            runner.measure_costs(3)
+            # rank r is r chunks behind rank 0 here; r extra steps bring every stage to the same chunk,
+            # which is what moving K/V state between stages requires
+            phase(3 + rank, resident, keep_full=False)
+            planned = runner.plan_ranges("block" if args.block_split == "measured-blocks" else "half")
+            runner.rebalance(planned, halves=True)
+            phase(max(args.warmup, 1) + 2 + (world - 1 - rank), resident)     # re-record graphs, stagger again
+            barrier()
+            ops.read_status(device)
 
         log = ops.LaunchLog(timed=not args.graphs)
         ops.set_launch_log(log)
@@ -845,7 +871,12 @@ def run_pipeline(args):
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
                          "traffic": None, "avg_launch_ms": att_ms, "flops_per_launch": att_flops},
             "cpu_baseline": None, "clocks": clocks,
-            "stage_blocks": ranges, "stage_compute_ms": [round(t.item(), 3) for t in per_stage], "stage_hop_bytes": rows * n_tok * MODEL_1P3B["dim"] * 2,
+            "block_split": args.block_split,
+            "stage_half_blocks": runner.half_ranges, "stage_blocks": [[a / 2, b / 2] for a, b in runner.half_ranges],
+            "stage_compute_ms": [round(t.item(), 3) for t in per_stage],
+            "stage_hop_bytes": rows * n_tok * MODEL_1P3B["dim"] * 2,
+            "reference_split": reference_split,
+            "measured_costs": getattr(runner, "last_costs", None),
         }
         args.emit(line)
     dist.destroy_process_group()
@@ -869,9 +900,13 @@ def main():
     ap.add_argument("--max-repeats", type=int, default=8)
     ap.add_argument("--no-graphs", dest="graphs", action="store_false",
                     help="launch every op of every step from Python instead of replaying steady steps from a CUDA graph")
-    ap.add_argument("--block-split", default="reference", choices=["reference", "balanced"],
-                    help="N>1: the reference's default block ranges (remainder on the first stages) or the "
-                         "remainder on the middle stages")
+    ap.add_argument("--block-split", default="measured",
+                    choices=["reference", "balanced", "measured", "measured-blocks"],
+                    help="N>1: reference = the reference's default block ranges (remainder on the first stages); "
+                         "balanced = remainder on the middle stages; measured = start on the reference's split, time "
+                         "one region there, then re-plan the ranges from measured per-half-block costs (stage "
+                         "boundaries may fall inside a block) and move the blocks; measured-blocks = the same with "
+                         "boundaries at whole blocks")
     ap.add_argument("--model", default="1.3b", choices=["1.3b", "14b"],
                     help="1.3b is the headline workload; 14b = 40 blocks, dim 5120, 40 heads, 4 denoise levels")
     args = ap.parse_args()

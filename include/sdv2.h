@@ -145,6 +145,32 @@ int sdv2_norm_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_
                              int* status_dev, void* stream);
 
 /*
+ * Data-dependent half of the sink + ring slot logic, on the device, for the adaptive sink refresh
+ * (models/wan/causal_model.py:284-299 for the test, :302-337 for the queue): one launch per layer
+ * decides for every cache row whether a sink frame is refreshed, updates the row's evict queue and
+ * writes the parameter array that sdv2_rope_kv_append_indirect reads, so that no similarity, queue
+ * entry or slot is ever read back by the host.
+ *
+ * sim_dev: device [rows][sink_frames], bf16 or f32 (sim_dtype): (cos(K sink mean, K new mean) +
+ *   cos(V sink mean, V new mean)) / 2 as the caller computed it; NULL or sink_frames == 0: no test.
+ *   A row whose smallest entry is below `threshold` (compared in sim_dtype, first minimum wins) gets
+ *   (argmin + 1) * frame_tokens pushed at the head of its queue.
+ * queue_dev: device int64 [rows][1 + queue_cap]: length, then the entries; updated in place.
+ * host_inputs / host_inputs_dev: the data-independent inputs, int64 [7][rows] - start frame | global
+ *   end value | local end value | evict branch (0/1) | pop the head (0/1) | rolling end to register or
+ *   -1 | slot of the append branch - on the host (copied into the launch) or on the device (read when
+ *   the kernel runs: for launches recorded in a CUDA graph); exactly one of the two is given.
+ * step_params_dev: out, device int64 [4][rows]: start frame | slot | global end | local end.
+ * An empty queue in the evict branch (the reference raises there) or a queue overflow writes slot -1,
+ * which the append kernel refuses, and reports through *status_dev (sdv2_read_status answers
+ * SDV2_ERR_INVALID_ARG).
+ */
+int sdv2_ring_plan_adaptive(const void* sim_dev, int sim_dtype, int rows, int sink_frames, float threshold,
+                            int64_t* queue_dev, int queue_cap, int64_t frame_tokens, int64_t new_tokens,
+                            const int64_t* host_inputs, const int64_t* host_inputs_dev,
+                            int64_t* step_params_dev, int* status_dev, void* stream);
+
+/*
  * Attention of the new queries over the wrapped cache: out[b] = softmax(q[b] k[b,:L_b]^T * scale)
  * v[b,:L_b] with L_b = seq_lens[b], no causal or window mask (the window is the cache content).
  *

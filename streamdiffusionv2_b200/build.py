@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsdv2.so")
-SOURCES = ["api.cu", "rope_append.cu", "attn_simt.cu", "attn_tcgen05.cu", "noalloc.cu", "block_elementwise.cu"]
+SOURCES = ["api.cu", "rope_append.cu", "attn_simt.cu", "attn_tcgen05.cu", "noalloc.cu", "block_elementwise.cu", "ring_plan.cu"]
 HEADERS = ["ptx.cuh", "sdv2_internal.h", os.path.join("..", "..", "include", "sdv2.h")]
 
 

@@ -75,22 +75,26 @@ class HostStarts:
         return list(self.values)
 
 
-def _adaptive_front(kv_cache, roped_k, v, i, sink_size, frame_tokens, thr) -> Optional[int]:
-    """Adaptive sink refresh test of row i, as the reference states it (causal_model.py:284-299);
-    data dependent, so it reads one scalar back."""
+def adaptive_similarities(kv_cache, roped_k, v, sink_size: int, frame_tokens: int) -> torch.Tensor:
+    """[rows, sink] similarity of the new frame to every sink frame, for all rows at once, with the
+    reference's own operations (causal_model.py:286-296): cosine similarity of the per-frame mean K,
+    the same for V, averaged.  Rows are independent (row i reads cache row i only).  Stays on the
+    device: the threshold test and everything that follows from it run in the plan kernel."""
+    rows = roped_k.shape[0]
     sink_tokens = sink_size * frame_tokens
-    k_sink = kv_cache["k"][i:i + 1, :sink_tokens].reshape(sink_size, frame_tokens, -1).mean(1)
-    k_new = roped_k[i:i + 1].reshape(1, frame_tokens, -1).mean(1)
+    k_sink = kv_cache["k"][:rows, :sink_tokens].reshape(rows, sink_size, frame_tokens, -1).mean(2)
+    k_new = roped_k.reshape(rows, 1, frame_tokens, -1).mean(2)
+    v_sink = kv_cache["v"][:rows, :sink_tokens].reshape(rows, sink_size, frame_tokens, -1).mean(2)
+    v_new = v.reshape(rows, 1, frame_tokens, -1).mean(2)
     k_sim = torch.cosine_similarity(k_sink, k_new, dim=-1)
-    v_sink = kv_cache["v"][i:i + 1, :sink_tokens].reshape(sink_size, frame_tokens, -1).mean(1)
-    v_new = v[i:i + 1].reshape(1, frame_tokens, -1).mean(1)
     v_sim = torch.cosine_similarity(v_sink, v_new, dim=-1)
-    avg = (k_sim + v_sim) / 2
-    lo, arg = torch.min(avg, dim=0)
-    lo, arg = lo.item(), int(arg.item())
-    if lo < thr:
-        return (arg + 1) * frame_tokens
-    return None
+    return ((k_sim + v_sim) / 2).contiguous()
+
+
+def sync_evict_queue(attn_module) -> None:
+    """Refresh `attn_module.evict_idx` (the reference's attribute) from the device-resident queue that
+    the adaptive sink path keeps (one read-back); no-op for modules whose queue lives on the host."""
+    RingState.sync_queue(attn_module)
 
 
 def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_start, norm=None):
@@ -113,11 +117,9 @@ def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_
     sink_tokens = attn_module.sink_size * frame_tokens
     adaptive = sink_tokens > 0 and attn_module.adapt_sink_thr > -1 and n_new <= frame_tokens
 
-    if _step_recorder is not None and adaptive:
-        raise RuntimeError("the adaptive sink test reads the device back and cannot be recorded in a graph")
+    extra = {} if norm is None else {"norm": norm}
     if not adaptive:
         dst, seq_lens = state.plan(kv_cache, attn_module, starts, n_new, frame_tokens)
-        extra = {} if norm is None else {"norm": norm}
         if _step_recorder is not None:
             extra["step_params"] = _step_recorder.layer_params(attn_module, kv_cache, start_frames, dst, state,
                                                                seq_lens, n_new, frame_tokens)
@@ -125,25 +127,35 @@ def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_
                                      dst, index_tensors=index_tensors,
                                      index_values=(state.global_end, state.local_end), **extra)
     else:
-        # the slot of row i depends on roped k and on the cache as rows < i left it: rope into a
-        # staging chunk first, then test and place row by row
-        stage_k = torch.empty_like(k, memory_format=torch.contiguous_format)
-        stage_v = torch.empty_like(v, memory_format=torch.contiguous_format)
-        roped_q = ops.rope_kv_append(q, k, v, stage_k, stage_v, table, (f, gh, gw), start_frames, [0] * B,
-                                     **({} if norm is None else {"norm": norm}))
-        state._ensure_queues(kv_cache, attn_module)
+        # The slot of a row depends on the data (roped k against the sink frames already in the cache), so the
+        # queue lives on the device: rope into a staging chunk, compute the similarities there, let the plan
+        # kernel decide the slots, then run the append itself with the slots read from device memory.  Nothing
+        # is read back.  Everything that does not depend on the data is still decided here, on host integers.
+        if n_new != frame_tokens:
+            raise RuntimeError("the adaptive sink test compares whole frames: one latent frame per chunk")
+        queue = RingState.push_queue(kv_cache, attn_module, q.device)
+        stage_k = torch.empty((B, n_new, H, D), dtype=k.dtype, device=k.device)
+        stage_v = torch.empty((B, n_new, H, D), dtype=v.dtype, device=v.device)
+        ops.rope_kv_append(q, k, v, stage_k, stage_v, table, (f, gh, gw), start_frames, [0] * B, **extra)
+        sim = adaptive_similarities(kv_cache, stage_k, stage_v, attn_module.sink_size, frame_tokens)
+        inputs = [[], [], [], [], [], [], []]
         seq_lens = []
         for i in range(B):
-            front = _adaptive_front(kv_cache, stage_k, stage_v, i, attn_module.sink_size, frame_tokens,
-                                    attn_module.adapt_sink_thr)
-            b0, le = state.plan_row(kv_cache, attn_module, i, starts[i], n_new, frame_tokens, front)
-            kv_cache["k"][i, b0:b0 + n_new] = stage_k[i]
-            kv_cache["v"][i, b0:b0 + n_new] = stage_v[i]
+            evict, pop, push_value, begin, le = state.plan_row_split(kv_cache, attn_module, i, starts[i], n_new,
+                                                                     frame_tokens)
+            for lst, val in zip(inputs, (start_frames[i], state.global_end[i], le, int(evict), int(pop), push_value,
+                                         begin)):
+                lst.append(val)
             seq_lens.append(le)
-        g, l = index_tensors
-        g.copy_(torch.tensor(state.global_end[:g.numel()], dtype=torch.int64), non_blocking=True)
-        l.copy_(torch.tensor(state.local_end[:l.numel()], dtype=torch.int64), non_blocking=True)
-        state._sig = RingState._signature(kv_cache)
+        if _step_recorder is not None:
+            step_params, plan_kw = _step_recorder.adaptive_layer_params(attn_module, kv_cache, inputs, seq_lens,
+                                                                        n_new, frame_tokens)
+        else:
+            step_params = torch.empty((4, B), dtype=torch.int64, device=q.device)
+            plan_kw = {"host_inputs": inputs}
+        ops.ring_plan_adaptive(sim, attn_module.adapt_sink_thr, queue, frame_tokens, n_new, step_params, **plan_kw)
+        roped_q = ops.rope_kv_append(q, k, v, kv_cache["k"], kv_cache["v"], table, (f, gh, gw), start_frames,
+                                     [0] * B, index_tensors=index_tensors, step_params=step_params, **extra)
 
     if q.dtype == torch.bfloat16:
         out = ops.attn_kvcache(roped_q, kv_cache["k"], kv_cache["v"], seq_lens)

@@ -386,6 +386,40 @@ int sdv2_selftest_umma(const void* a_dev, const void* b_dev, const void* p_dev, 
   return e == cudaSuccess ? SDV2_OK : cuda_fail(e);
 }
 
+int sdv2_ring_plan_adaptive(const void* sim_dev, int sim_dtype, int rows, int sink_frames, float threshold,
+                            int64_t* queue_dev, int queue_cap, int64_t frame_tokens, int64_t new_tokens,
+                            const int64_t* host_inputs, const int64_t* host_inputs_dev, int64_t* step_params_dev,
+                            int* status_dev, void* stream) {
+  if (queue_dev == nullptr || step_params_dev == nullptr) return SDV2_ERR_INVALID_ARG;
+  if ((host_inputs == nullptr) == (host_inputs_dev == nullptr)) return SDV2_ERR_INVALID_ARG;
+  if (rows <= 0 || queue_cap <= 0 || frame_tokens <= 0 || new_tokens <= 0 || sink_frames < 0) return SDV2_ERR_INVALID_ARG;
+  if (rows > SDV2_MAX_ROWS) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  if (sim_dev != nullptr && sim_dtype != SDV2_DTYPE_BF16 && sim_dtype != SDV2_DTYPE_F32) return SDV2_ERR_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(queue_dev) | reinterpret_cast<uintptr_t>(step_params_dev) |
+       reinterpret_cast<uintptr_t>(host_inputs_dev)) & 7u)
+    return SDV2_ERR_MISALIGNED;
+  sdv2::RingPlanParams p;
+  memset(&p, 0, sizeof(p));
+  p.sim = sink_frames > 0 ? sim_dev : nullptr;
+  p.dtype = sim_dtype;
+  p.rows = rows;
+  p.sink_frames = sink_frames;
+  p.threshold = threshold;
+  p.queue = queue_dev;
+  p.queue_cap = queue_cap;
+  p.frame_tokens = frame_tokens;
+  p.sink_tokens = frame_tokens * sink_frames;
+  p.new_tokens = new_tokens;
+  p.host_dev = host_inputs_dev;
+  if (host_inputs != nullptr)
+    for (int w = 0; w < sdv2::kRingPlanInputs; ++w)
+      for (int b = 0; b < rows; ++b) p.host_val[w][b] = host_inputs[w * rows + b];
+  p.step_params = step_params_dev;
+  p.status = status_dev;
+  cudaError_t e = sdv2::launch_ring_plan(p, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? SDV2_OK : cuda_fail(e);
+}
+
 int sdv2_selftest_wait_timeout(int* status_dev, long long budget_cycles, void* stream) {
   if (status_dev == nullptr) return SDV2_ERR_INVALID_ARG;
   if (reinterpret_cast<uintptr_t>(status_dev) & 3u) return SDV2_ERR_MISALIGNED;

@@ -185,7 +185,8 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 }
 
 // Stage layout: q rows | k rows | v rows (tile_tokens x row_bytes each) | multiplier rows
-// (tile_tokens x half complex doubles) | with kNorm: 1 / rms of every q row, then of every k row.  The producer group (the last warps) issues the bulk copies
+// (tile_tokens x half complex doubles) | with kNorm: 1 / rms of every q row, then of every k row, then the
+// 8 group sums of every row from which they are folded.  The producer group (the last warps) issues the bulk copies
 // of a tile and builds the tile's multiplier rows from the rope table; each of its warps then
 // arrives on the stage's "full" barrier, which completes once the copied bytes are in as well.
 // Barrier over `threads` threads (a multiple of 32) that also ANDs a flag over them.
@@ -325,30 +326,38 @@ rope_kv_append_staged_kernel(const __grid_constant__ AppendParams p) {
       const uint8_t* sq = gbase + s * stage_bytes;
       const float* rstd_s = reinterpret_cast<const float*>(sq + mult_off + tile_tokens * mult_row_bytes);
       if (kNorm) {
-        // 1 / rms of every staged q and k row, one warp per row, summed in the order sdv2_rmsnorm uses
+        // 1 / rms of every staged q and k row, summed in the order sdv2_rmsnorm uses.  Pass 1, all consumer
+        // threads: a task is one of the norm kernel's 256 "thread slots" of one row (vectors slot, slot + 256,
+        // ... chained); 32 consecutive slots sit in one warp and are folded with the xor butterfly into one
+        // group sum.  Pass 2, one thread per row: the 8 group sums through the fixed tree, then 1 / rms.
         float* rstd_w = const_cast<float*>(rstd_s);
-        for (int r = warp; ok && r < 2 * n; r += consumer_warps) {
-          const int which = r >= n ? 1 : 0;
-          const uint8_t* rowp = sq + which * tensor_stride + (r - which * n) * row_bytes;
+        float* gsum = rstd_w + 2 * tile_tokens;                        // [2 * tile_tokens][8]
+        const int slots = min(256, (row_vecs + 31) & ~31);             // slots that hold at least one vector, per warp
+        if (ok) {
+          for (int task = threadIdx.x; task < 2 * n * slots; task += consumers) {
+            const int r = task / slots;                                // row: q rows first, then k rows
+            const int t = task - r * slots;
+            const int which = r >= n ? 1 : 0;
+            const uint8_t* rowp = sq + which * tensor_stride + (r - which * n) * row_bytes;
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int c = t + i * 256;
+              if (c < row_vecs) ss = rms_accumulate(ss, *reinterpret_cast<const uint4*>(rowp + c * 16));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) gsum[r * 8 + (t >> 5)] = ss;
+          }
+        }
+        ok = named_barrier_and(1, consumers, ok);   // consumers only; the producer group never joins
+        if (ok && threadIdx.x < 2 * n) {
           float g[8];
 #pragma unroll
-          for (int w = 0; w < 8; ++w) {
-            float ss = 0.f;
-            if (w * 32 < row_vecs) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int c = w * 32 + lane + i * 256;
-                if (c < row_vecs) ss = rms_accumulate(ss, *reinterpret_cast<const uint4*>(rowp + c * 16));
-              }
-#pragma unroll
-              for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            }
-            g[w] = ss;
-          }
-          if (lane == 0) rstd_w[r] = rms_rstd(rms_fold_groups(g), p.heads * p.head_dim, p.norm_eps);
+          for (int w = 0; w < 8; ++w) g[w] = w * 32 < slots ? gsum[threadIdx.x * 8 + w] : 0.f;
+          rstd_w[threadIdx.x] = rms_rstd(rms_fold_groups(g), p.heads * p.head_dim, p.norm_eps);
         }
-        // consumers only (the producer group never joins); a warp whose wait was abandoned still
-        // arrives, and everybody leaves together
+        // a warp whose wait was abandoned still arrives, and everybody leaves together
         ok = named_barrier_and(1, consumers, ok);
         if (!ok) break;
       }
@@ -430,7 +439,7 @@ cudaError_t launch_rope_kv_append(const AppendParams& p_in, int dtype, cudaStrea
   // threads and three stages must fit in shared memory; then more warps and larger tiles
   const uint32_t mult_row = static_cast<uint32_t>(p.half) * 16u;
   const bool norm = p.norm_q_weight != nullptr;
-  const uint32_t norm_row = norm ? 8u : 0u;   // two floats per token: 1 / rms of its q row and of its k row
+  const uint32_t norm_row = norm ? 8u + 64u : 0u;   // per token: 1 / rms of its q and k rows + 2 x 8 group sums
   int best_tt = 0, best_w = 0;
   double best_score = 0.0;
   for (int tt = 1; tt <= staged::kMaxTileTokens; ++tt) {

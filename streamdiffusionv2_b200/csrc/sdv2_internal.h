@@ -163,6 +163,21 @@ cudaError_t launch_umma_selftest(const CUtensorMap& tm_a, const CUtensorMap& tm_
                                  const void* p_dev, float* s_out, float* o_out, int* status,
                                  cudaStream_t stream);
 
+constexpr int kRingPlanInputs = 7;  // start frame | global end | local end | evict | pop | push value | append slot
+struct RingPlanParams {
+  const void* sim;       // [rows][sink_frames] similarities of the new frame to the sink frames, or null (no test)
+  int dtype, rows, sink_frames;
+  float threshold;
+  int64_t* queue;        // [rows][1 + queue_cap]: length, entries
+  int queue_cap;
+  int64_t frame_tokens, sink_tokens, new_tokens;
+  const int64_t* host_dev;                          // optional device copy of host_val, [kRingPlanInputs][rows]
+  int64_t host_val[kRingPlanInputs][SDV2_MAX_ROWS];
+  int64_t* step_params;  // out: [4][rows] for the append kernel
+  int* status;
+};
+cudaError_t launch_ring_plan(const RingPlanParams& p, cudaStream_t stream);
+
 cudaError_t launch_wait_timeout_selftest(int* status, long long budget_cycles, cudaStream_t stream);
 
 }  // namespace sdv2

@@ -170,6 +170,41 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
     return q_out
 
 
+def ring_plan_adaptive(sim: Optional[torch.Tensor], threshold: float, queue: torch.Tensor, frame_tokens: int,
+                       n_new: int, step_params: torch.Tensor, *, host_inputs: Optional[Sequence[Sequence[int]]] = None,
+                       host_inputs_dev: Optional[torch.Tensor] = None) -> None:
+    """One launch of the device-side slot logic for all rows of a layer (adaptive sink refresh).
+    sim: [rows, sink_frames] similarities on the device (bf16 / fp32) or None; queue: int64
+    [rows, 1 + cap] on the device, updated in place; host_inputs: 7 lists of `rows` ints (start frame,
+    global end, local end, evict, pop, push value, append slot) or, for a launch that is recorded in a
+    graph, the same as a device int64 [7, rows] tensor; step_params: device int64 [4, rows], written
+    for `rope_kv_append(step_params=...)`."""
+    rows = queue.shape[0]
+    if queue.dtype != torch.int64 or not queue.is_contiguous() or step_params.dtype != torch.int64 \
+            or not step_params.is_contiguous() or step_params.numel() != 4 * rows:
+        raise ValueError("queue / step_params must be contiguous int64 tensors")
+    sink = 0
+    sim_ptr, code = None, 0
+    if sim is not None:
+        if sim.shape[0] != rows or not sim.is_contiguous():
+            raise ValueError("sim must be a contiguous [rows, sink_frames] tensor")
+        sink, sim_ptr, code = sim.shape[1], sim.data_ptr(), N.dtype_code(sim.dtype)
+    hv = dev = None
+    if host_inputs_dev is not None:
+        if host_inputs_dev.dtype != torch.int64 or not host_inputs_dev.is_contiguous() \
+                or host_inputs_dev.numel() != 7 * rows:
+            raise ValueError("host_inputs_dev must be a contiguous int64 [7, rows] tensor")
+        dev = host_inputs_dev.data_ptr()
+    else:
+        hv = N.i64_array([int(x) for lst in host_inputs for x in lst])
+    with _Logged("ring_plan"):
+        rc = N.lib().sdv2_ring_plan_adaptive(sim_ptr, code, rows, sink, float(threshold), queue.data_ptr(),
+                                             queue.shape[1] - 1, int(frame_tokens), int(n_new), hv, dev,
+                                             step_params.data_ptr(), workspace(queue.device).data_ptr(),
+                                             N.stream_ptr(queue.device))
+    N.check(rc, "sdv2_ring_plan_adaptive")
+
+
 def can_fuse_norm(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, weight_q: torch.Tensor,
                   weight_k: torch.Tensor) -> bool:
     """Whether `rope_kv_append(norm=...)` serves these tensors: bf16 on CUDA, the heads of a token back

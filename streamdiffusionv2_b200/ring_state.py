@@ -109,9 +109,109 @@ class RingState:
         self.local_end[i] = le
         return begin, le
 
+    # ------------------------------------------------------------------ queue kept on the device
+    # With the adaptive sink test the evict queue depends on the data (causal_model.py:284-299), so a
+    # host-side queue would need a read-back per row per layer.  In that mode the queue lives in a
+    # device tensor [rows, 1 + QUEUE_CAP] (length, entries) that the plan kernel updates, kept on the
+    # attention module as `_sdv2_queue`; the module's `evict_idx` lists are then a stale copy until
+    # `sync_queue` refreshes them.  Everything else the slot logic decides does not depend on the
+    # data and stays on the host (`plan_row_split`).
+    QUEUE_CAP = 63
+
+    @staticmethod
+    def push_queue(kv_cache: dict, attn_module, device) -> torch.Tensor:
+        """Device copy of the module's queues (created from the host lists when there is none, or
+        when the number of cache rows changed); the device copy is authoritative afterwards."""
+        rows = kv_cache["k"].shape[0]
+        q = getattr(attn_module, "_sdv2_queue", None)
+        if q is not None and (q.shape[0] != rows or q.device != torch.device(device)):
+            RingState.pull_queue(attn_module)
+            q = None
+        if q is None:
+            RingState._ensure_queues(kv_cache, attn_module)
+            host = torch.zeros(rows, 1 + RingState.QUEUE_CAP, dtype=torch.int64)
+            for i, lst in enumerate(attn_module.evict_idx[:rows]):
+                if len(lst) > RingState.QUEUE_CAP:
+                    raise RuntimeError("evict queue longer than the device record")
+                host[i, 0] = len(lst)
+                if lst:
+                    host[i, 1:1 + len(lst)] = torch.tensor([int(x) for x in lst], dtype=torch.int64)
+            q = host.to(device)
+            attn_module._sdv2_queue = q
+        return q
+
+    @staticmethod
+    def sync_queue(attn_module) -> None:
+        """Refresh `attn_module.evict_idx` from the device queue (one read-back); the device copy
+        stays authoritative.  No-op when the queue lives on the host."""
+        q = getattr(attn_module, "_sdv2_queue", None)
+        if q is None:
+            return
+        host = q.cpu().tolist()
+        attn_module.evict_idx = [[int(x) for x in row[1:1 + int(row[0])]] for row in host]
+
+    @staticmethod
+    def pull_queue(attn_module) -> None:
+        """Bring the queue back to the host lists and drop the device copy (the host-integer slot
+        logic, block re-ownership and anything else that reads `evict_idx` call this first)."""
+        if getattr(attn_module, "_sdv2_queue", None) is not None:
+            RingState.sync_queue(attn_module)
+            attn_module._sdv2_queue = None
+
+    def plan_row_split(self, kv_cache: dict, attn_module, i: int, cs: int, n_new: int, frame_tokens: int):
+        """The data-independent part of `plan_row` for row i: everything but the queue.  Updates the
+        mirror and the step counter exactly as `plan_row` does and returns what the device-side queue
+        logic needs: (evict, pop, push_value, append_begin, seq_len) where `evict` selects the branch
+        (causal_model.py:302), `pop` says whether the head leaves the queue (:310-316), `push_value`
+        is the rolling end the append branch registers unless it is already the tail (-1: none,
+        :326-332) and `append_begin` the slot of the append branch."""
+        smax = kv_cache["k"].shape[1]
+        rows = kv_cache["k"].shape[0]
+        sink_tokens = attn_module.sink_size * frame_tokens
+        ce = cs + n_new
+        if ce > smax or self.local_end[i] >= smax:
+            evict, push_value, begin, le = True, -1, -1, smax
+            if rows == 1 and kv_cache["current_step"] > 1:
+                kv_cache["current_step"] -= 1
+                pop = False
+            else:
+                kv_cache["current_step"] = kv_cache["total_steps"]
+                pop = True
+        else:
+            evict, pop = False, False
+            le = self.local_end[i] + ce - self.global_end[i]
+            rolling_end = ce + n_new
+            push_value = rolling_end if sink_tokens < rolling_end <= smax else -1
+            begin = le - n_new
+            if begin < 0 or begin + n_new > smax:
+                raise RuntimeError(
+                    f"cache slot [{begin}, {begin + n_new}) of row {i} lies outside the {smax}-token cache")
+        self.global_end[i] = ce
+        self.local_end[i] = le
+        return evict, pop, push_value, begin, le
+
+    @staticmethod
+    def queue_step(queue: List[int], front: Optional[int], evict: bool, pop: bool, push_value: int,
+                   append_begin: int, n_new: int, sink_tokens: int) -> int:
+        """The queue half of the slot logic, as the device plan kernel runs it (this host version is
+        the specification the kernel follows and what the CPU tests exercise).  Returns the slot."""
+        if front is not None:
+            queue.insert(0, int(front))
+        if evict:
+            target_end = queue[0]
+            if pop:
+                head = queue.pop(0)
+                if head > sink_tokens:
+                    queue.append(head)
+            return target_end - n_new
+        if push_value >= 0 and (not queue or queue[-1] != push_value):
+            queue.append(push_value)
+        return append_begin
+
     def plan(self, kv_cache: dict, attn_module, current_start: Sequence[int], n_new: int,
              frame_tokens: int) -> Tuple[List[int], List[int]]:
         """Slot decisions for all rows, in row order.  Returns (dst_begin, seq_lens)."""
+        self.pull_queue(attn_module)
         self._ensure_queues(kv_cache, attn_module)
         dst_begin, seq_lens = [], []
         for i, cs in enumerate(current_start):

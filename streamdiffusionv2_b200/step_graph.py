@@ -24,6 +24,7 @@ from . import ops
 from .ring_state import RingState
 
 _PINNED_SLOTS = 4
+_STEP, _PLAN = 4, 7       # per layer and row: 4 values the append kernel reads, 7 inputs of the adaptive plan kernel
 
 
 class _Recorder:
@@ -44,11 +45,26 @@ class _Recorder:
             self.seq_lens, self.n_new, self.frame_tokens = list(seq_lens), n_new, frame_tokens
         elif list(seq_lens) != self.seq_lens:
             raise RuntimeError("layers disagree on the attention lengths; step cannot be recorded")
-        self.layers.append((attn_module, kv_cache))
+        self.layers.append((attn_module, kv_cache, False))
         rows = len(dst)
-        self.host[i] = torch.tensor([start_frames, dst, state.global_end[:rows], state.local_end[:rows]],
-                                    dtype=torch.int64)
-        return self.params_dev[i]
+        self.host[i, :_STEP] = torch.tensor([start_frames, dst, state.global_end[:rows], state.local_end[:rows]],
+                                            dtype=torch.int64)
+        return self.params_dev[i, :_STEP]
+
+    def adaptive_layer_params(self, attn_module, kv_cache, inputs, seq_lens, n_new, frame_tokens):
+        """A layer with the adaptive sink test: its slots are decided on the device by the plan kernel,
+        which reads the data-independent inputs from this layer's slice of the parameter array and
+        writes the four values the append kernel reads into the slice in front of it."""
+        i = len(self.layers)
+        if i >= self.params_dev.shape[0]:
+            raise RuntimeError("more attention layers ran than the graph was sized for")
+        if self.seq_lens is None:
+            self.seq_lens, self.n_new, self.frame_tokens = list(seq_lens), n_new, frame_tokens
+        elif list(seq_lens) != self.seq_lens:
+            raise RuntimeError("layers disagree on the attention lengths; step cannot be recorded")
+        self.layers.append((attn_module, kv_cache, True))
+        self.host[i, _STEP:] = torch.tensor(inputs, dtype=torch.int64)
+        return self.params_dev[i, :_STEP], {"host_inputs_dev": self.params_dev[i, _STEP:]}
 
 
 class _Recorded:
@@ -77,8 +93,8 @@ class StepGraphs:
     def __init__(self, device: torch.device, max_layers: int, rows: int):
         self.device = torch.device(device)
         self.rows = rows
-        self.params_dev = torch.zeros((max_layers, 4, rows), dtype=torch.int64, device=self.device)
-        self._pinned = [torch.zeros((max_layers, 4, rows), dtype=torch.int64).pin_memory()
+        self.params_dev = torch.zeros((max_layers, _STEP + _PLAN, rows), dtype=torch.int64, device=self.device)
+        self._pinned = [torch.zeros((max_layers, _STEP + _PLAN, rows), dtype=torch.int64).pin_memory()
                         for _ in range(_PINNED_SLOTS)]
         self._pinned_done: List[Optional[torch.cuda.Event]] = [None] * _PINNED_SLOTS
         self._turn = 0
@@ -94,17 +110,16 @@ class StepGraphs:
     @staticmethod
     def steady(layers: Sequence[tuple], starts: Sequence[int], n_new: int) -> bool:
         """True when every row of every layer takes the wrapped-cache branch of the slot logic,
-        i.e. attends the whole cache (causal_model.py:301-322), no layer uses the adaptive sink
-        test, and (where the layer's crossattn_cache is given as a third entry) the text K/V are
-        cached, so that the step launches exactly what a recorded one launched.  Nothing is modified."""
+        i.e. attends the whole cache (causal_model.py:301-322), and (where the layer's crossattn_cache
+        is given as a third entry) the text K/V are cached, so that the step launches exactly what a
+        recorded one launched.  Layers with the adaptive sink test qualify too: their data-dependent
+        slot choice runs on the device, inside the recording.  Nothing is modified."""
         for entry in layers:
             module, kv = entry[0], entry[1]
             if len(entry) > 2 and entry[2] is not None and not entry[2].get("is_init", False):
                 return False
             if kv is None:
                 continue
-            if module.sink_size > 0 and module.adapt_sink_thr > -1:
-                return False
             st = RingState.of(kv)
             smax = kv["k"].shape[1]
             for i, cs in enumerate(starts):
@@ -125,14 +140,21 @@ class StepGraphs:
         start_frames = [int(s) // ft for s in starts]
         rows = len(starts)
         flat: List[List[int]] = []
-        for module, kv in rec.layers:
+        zeros4, zeros7 = [0] * (_STEP * rows), [0] * (_PLAN * rows)
+        for module, kv, adaptive in rec.layers:
             st = RingState.of(kv)
-            dst, lens = st.plan(kv, module, starts, rec.n_new, ft)
+            if adaptive:
+                cols = [st.plan_row_split(kv, module, i, int(starts[i]), rec.n_new, ft) for i in range(rows)]
+                lens = [c[4] for c in cols]
+                flat.append(zeros4 + start_frames + st.global_end[:rows] + lens + [int(c[0]) for c in cols]
+                            + [int(c[1]) for c in cols] + [c[2] for c in cols] + [c[3] for c in cols])
+            else:
+                dst, lens = st.plan(kv, module, starts, rec.n_new, ft)
+                flat.append(start_frames + dst + st.global_end[:rows] + st.local_end[:rows] + zeros7)
             if lens != rec.seq_lens:
                 raise RuntimeError("slot state left the recorded steady state during a replayed step")
-            flat.append(start_frames + dst + st.global_end[:rows] + st.local_end[:rows])
         n = len(flat)
-        host[:n] = torch.tensor(flat, dtype=torch.int64).view(n, 4, rows)
+        host[:n] = torch.tensor(flat, dtype=torch.int64).view(n, _STEP + _PLAN, rows)
         self.params_dev[:n].copy_(host[:n], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()

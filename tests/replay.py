@@ -77,5 +77,6 @@ def replay_cuda(case: dict, device="cuda"):
         grid = torch.tensor([[frames, h, w]] * len(starts), dtype=torch.long)
         cs = torch.tensor(starts, dtype=torch.long, device=device)
         out = ca.cached_attention(mod, q, k, v, grid, freqs, kv, cs)
+        ca.sync_evict_queue(mod)      # with the adaptive sink test the queue lives on the device
         yield i, out, kv, mod
         i += 1

@@ -92,8 +92,8 @@ def test_step_graph_steady_state_predicate_matches_the_slot_logic():
         seen_steady += steady
         start += n_new
     assert seen_steady >= 8
-    mod.adapt_sink_thr = 0.5                      # the adaptive sink test reads the device: never recorded
-    assert not StepGraphs.steady([(mod, kv)], history, n_new)
+    mod.adapt_sink_thr = 0.5                      # the adaptive sink test runs on the device: it records too
+    assert StepGraphs.steady([(mod, kv)], history, n_new)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -187,3 +187,42 @@ def test_collective_writes_to_index_tensors_need_and_get_invalidation():
     # after the hooked broadcast the receiver plans its next chunk from the donor's values
     assert ge == [36] and dst == [24] and lens == [36]
     assert res[0][2][1:] == ([36], [24], [36])
+
+
+def test_split_slot_logic_equals_the_whole_one_with_adaptive_fronts():
+    """With the adaptive sink test the queue is updated on the device and the rest of the slot logic
+    on the host.  The two halves together (`plan_row_split` + `queue_step`, the latter being the
+    host statement of what the plan kernel does) must equal the reference logic (`plan_row`, pinned
+    by the traces above) for any pattern of adaptive insertions."""
+    import random
+    from oracle import causal_attention_oracle as orc
+    rnd = random.Random(3)
+    for rows, frames, cache_frames, sink, total in ((2, 1, 6, 3, 2), (1, 1, 6, 3, 2), (3, 1, 8, 2, 3), (2, 1, 9, 1, 2)):
+        fs, n_new = 6, frames * 6
+        smax = cache_frames * fs
+        mk = lambda: {"k": torch.empty(rows, smax, 1, 0), "v": torch.empty(rows, smax, 1, 0),
+                      "global_end_index": torch.zeros(rows, dtype=torch.long),
+                      "local_end_index": torch.zeros(rows, dtype=torch.long), "total_steps": total, "current_step": total}
+        kv_a, kv_b = mk(), mk()
+        mod_a, mod_b = _Mod(sink), _Mod(sink)
+        st_ref = orc.RingLayerState(smax, rows, total_steps=total, current_step=total)
+        orc._ensure_queues(st_ref)
+        start, starts = 0, [0] * rows
+        for step in range(60):
+            if start // fs >= 20:
+                start = smax - fs
+            starts = [start] + starts[:-1]
+            fronts = [((rnd.randrange(sink) + 1) * fs if rnd.random() < 0.3 else None) for _ in range(rows)]
+            sa, sb = RingState.of(kv_a), RingState.of(kv_b)
+            RingState._ensure_queues(kv_a, mod_a)
+            RingState._ensure_queues(kv_b, mod_b)
+            for i in range(rows):
+                want = sa.plan_row(kv_a, mod_a, i, starts[i], n_new, fs, fronts[i])
+                ev, pop, push, begin, le = sb.plan_row_split(kv_b, mod_b, i, starts[i], n_new, fs)
+                dst = RingState.queue_step(mod_b.evict_idx[i], fronts[i], ev, pop, push, begin, n_new, sink * fs)
+                assert (dst, le) == want, (step, i)
+                assert orc.ring_plan_row(st_ref, i, starts[i], n_new, fs, sink, fronts[i]) == want
+            assert mod_a.evict_idx == mod_b.evict_idx == st_ref.evict_idx
+            assert sa.global_end == sb.global_end and sa.local_end == sb.local_end
+            assert kv_a["current_step"] == kv_b["current_step"] == st_ref.current_step
+            start += n_new
