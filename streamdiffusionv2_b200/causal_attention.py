@@ -134,10 +134,6 @@ def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_
         if n_new != frame_tokens:
             raise RuntimeError("the adaptive sink test compares whole frames: one latent frame per chunk")
         queue = RingState.push_queue(kv_cache, attn_module, q.device)
-        stage_k = torch.empty((B, n_new, H, D), dtype=k.dtype, device=k.device)
-        stage_v = torch.empty((B, n_new, H, D), dtype=v.dtype, device=v.device)
-        ops.rope_kv_append(q, k, v, stage_k, stage_v, table, (f, gh, gw), start_frames, [0] * B, **extra)
-        sim = adaptive_similarities(kv_cache, stage_k, stage_v, attn_module.sink_size, frame_tokens)
         inputs = [[], [], [], [], [], [], []]
         seq_lens = []
         for i in range(B):
@@ -147,12 +143,17 @@ def cached_attention(attn_module, q, k, v, grid_sizes, freqs, kv_cache, current_
                                          begin)):
                 lst.append(val)
             seq_lens.append(le)
-        if _step_recorder is not None:
-            step_params, plan_kw = _step_recorder.adaptive_layer_params(attn_module, kv_cache, inputs, seq_lens,
-                                                                        n_new, frame_tokens)
+        stage_kw = dict(extra)
+        if _step_recorder is not None:      # a recorded step must not carry this step's start frames by value
+            step_params, plan_kw, stage_kw["step_params"] = _step_recorder.adaptive_layer_params(
+                attn_module, kv_cache, inputs, seq_lens, n_new, frame_tokens)
         else:
             step_params = torch.empty((4, B), dtype=torch.int64, device=q.device)
             plan_kw = {"host_inputs": inputs}
+        stage_k = torch.empty((B, n_new, H, D), dtype=k.dtype, device=k.device)
+        stage_v = torch.empty((B, n_new, H, D), dtype=v.dtype, device=v.device)
+        ops.rope_kv_append(q, k, v, stage_k, stage_v, table, (f, gh, gw), start_frames, [0] * B, **stage_kw)
+        sim = adaptive_similarities(kv_cache, stage_k, stage_v, attn_module.sink_size, frame_tokens)
         ops.ring_plan_adaptive(sim, attn_module.adapt_sink_thr, queue, frame_tokens, n_new, step_params, **plan_kw)
         roped_q = ops.rope_kv_append(q, k, v, kv_cache["k"], kv_cache["v"], table, (f, gh, gw), start_frames,
                                      [0] * B, index_tensors=index_tensors, step_params=step_params, **extra)

@@ -24,7 +24,10 @@ from . import ops
 from .ring_state import RingState
 
 _PINNED_SLOTS = 4
-_STEP, _PLAN = 4, 7       # per layer and row: 4 values the append kernel reads, 7 inputs of the adaptive plan kernel
+# per layer and row: 4 values the append kernel reads, 7 inputs of the adaptive plan kernel, 4 values for the
+# append launch that ropes into the staging chunk in front of the adaptive test (start frame, slot 0, unused)
+_STEP, _PLAN, _STAGE = 4, 7, 4
+_ALL = _STEP + _PLAN + _STAGE
 
 
 class _Recorder:
@@ -54,7 +57,9 @@ class _Recorder:
     def adaptive_layer_params(self, attn_module, kv_cache, inputs, seq_lens, n_new, frame_tokens):
         """A layer with the adaptive sink test: its slots are decided on the device by the plan kernel,
         which reads the data-independent inputs from this layer's slice of the parameter array and
-        writes the four values the append kernel reads into the slice in front of it."""
+        writes the four values the append kernel reads into the slice in front of it; the append
+        launch that ropes the new frame into the staging chunk reads its start frames from a third
+        slice.  Returns (step_params, keyword for the plan kernel, staging step_params)."""
         i = len(self.layers)
         if i >= self.params_dev.shape[0]:
             raise RuntimeError("more attention layers ran than the graph was sized for")
@@ -63,8 +68,11 @@ class _Recorder:
         elif list(seq_lens) != self.seq_lens:
             raise RuntimeError("layers disagree on the attention lengths; step cannot be recorded")
         self.layers.append((attn_module, kv_cache, True))
-        self.host[i, _STEP:] = torch.tensor(inputs, dtype=torch.int64)
-        return self.params_dev[i, :_STEP], {"host_inputs_dev": self.params_dev[i, _STEP:]}
+        rows = len(inputs[0])
+        self.host[i, _STEP:_STEP + _PLAN] = torch.tensor(inputs, dtype=torch.int64)
+        self.host[i, _STEP + _PLAN:] = torch.tensor([inputs[0], [0] * rows, [0] * rows, [0] * rows], dtype=torch.int64)
+        return (self.params_dev[i, :_STEP], {"host_inputs_dev": self.params_dev[i, _STEP:_STEP + _PLAN]},
+                self.params_dev[i, _STEP + _PLAN:])
 
 
 class _Recorded:
@@ -93,8 +101,8 @@ class StepGraphs:
     def __init__(self, device: torch.device, max_layers: int, rows: int):
         self.device = torch.device(device)
         self.rows = rows
-        self.params_dev = torch.zeros((max_layers, _STEP + _PLAN, rows), dtype=torch.int64, device=self.device)
-        self._pinned = [torch.zeros((max_layers, _STEP + _PLAN, rows), dtype=torch.int64).pin_memory()
+        self.params_dev = torch.zeros((max_layers, _ALL, rows), dtype=torch.int64, device=self.device)
+        self._pinned = [torch.zeros((max_layers, _ALL, rows), dtype=torch.int64).pin_memory()
                         for _ in range(_PINNED_SLOTS)]
         self._pinned_done: List[Optional[torch.cuda.Event]] = [None] * _PINNED_SLOTS
         self._turn = 0
@@ -140,21 +148,22 @@ class StepGraphs:
         start_frames = [int(s) // ft for s in starts]
         rows = len(starts)
         flat: List[List[int]] = []
-        zeros4, zeros7 = [0] * (_STEP * rows), [0] * (_PLAN * rows)
+        zeros4, zeros11, zeros3 = [0] * (_STEP * rows), [0] * ((_PLAN + _STAGE) * rows), [0] * (3 * rows)
         for module, kv, adaptive in rec.layers:
             st = RingState.of(kv)
             if adaptive:
                 cols = [st.plan_row_split(kv, module, i, int(starts[i]), rec.n_new, ft) for i in range(rows)]
                 lens = [c[4] for c in cols]
                 flat.append(zeros4 + start_frames + st.global_end[:rows] + lens + [int(c[0]) for c in cols]
-                            + [int(c[1]) for c in cols] + [c[2] for c in cols] + [c[3] for c in cols])
+                            + [int(c[1]) for c in cols] + [c[2] for c in cols] + [c[3] for c in cols]
+                            + start_frames + zeros3)
             else:
                 dst, lens = st.plan(kv, module, starts, rec.n_new, ft)
-                flat.append(start_frames + dst + st.global_end[:rows] + st.local_end[:rows] + zeros7)
+                flat.append(start_frames + dst + st.global_end[:rows] + st.local_end[:rows] + zeros11)
             if lens != rec.seq_lens:
                 raise RuntimeError("slot state left the recorded steady state during a replayed step")
         n = len(flat)
-        host[:n] = torch.tensor(flat, dtype=torch.int64).view(n, _STEP + _PLAN, rows)
+        host[:n] = torch.tensor(flat, dtype=torch.int64).view(n, _ALL, rows)
         self.params_dev[:n].copy_(host[:n], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()

@@ -455,3 +455,61 @@ def test_fused_norm_append_equals_rmsnorm_then_append_bit_for_bit(B, N, H, grid,
     want = orc.rope_apply(qn.cpu(), grid, orc.rope_table(D), sf)
     assert torch.equal(rq2.cpu().view(torch.int16), want.view(torch.int16))
     ops.read_status(torch.device("cuda"))
+
+
+def test_device_plan_kernel_follows_the_host_statement_of_the_queue_logic():
+    """The kernel that keeps the evict queue on the device (adaptive sink refresh) against
+    `RingState.queue_step`, its host-side specification (itself checked against the oracle's slot
+    logic on the CPU): random similarities, branches, pops and pushes over many calls, both ways of
+    passing the host inputs, bf16 and fp32 similarities."""
+    import random
+    from streamdiffusionv2_b200.ring_state import RingState
+    ops = _ops()
+    dev = torch.device("cuda")
+    rnd = random.Random(9)
+    for dtype in (torch.bfloat16, torch.float32):
+        rows, sink, fs, n_new, thr = 5, 3, 60, 60, 0.2
+        cap = RingState.QUEUE_CAP
+        queues = [[(j + 4) * fs for j in range(rnd.randrange(1, 6))] for _ in range(rows)]
+        qdev = torch.zeros(rows, 1 + cap, dtype=torch.int64)
+        for i, lst in enumerate(queues):
+            qdev[i, 0] = len(lst)
+            qdev[i, 1:1 + len(lst)] = torch.tensor(lst)
+        qdev = qdev.to(dev)
+        step = torch.zeros(4, rows, dtype=torch.int64, device=dev)
+        for call in range(40):
+            sim = (torch.rand(rows, sink) * 0.6).to(dtype)
+            inputs = [[rnd.randrange(900) for _ in range(rows)], [rnd.randrange(10 ** 6) for _ in range(rows)],
+                      [rnd.randrange(10 ** 6) for _ in range(rows)], [], [], [], []]
+            want_slots = []
+            for i in range(rows):
+                evict = bool(queues[i]) and rnd.random() < 0.6
+                pop = evict and rnd.random() < 0.7
+                push = -1 if evict or rnd.random() < 0.3 else (rnd.randrange(4, 12)) * fs
+                begin = rnd.randrange(0, 500)
+                for lst, val in zip(inputs[3:], (int(evict), int(pop), push, begin)):
+                    lst.append(val)
+                row = sim[i].float()
+                lo = float(row.min())
+                thr_t = float(torch.tensor(thr, dtype=dtype))
+                front = (int(torch.argmin(row)) + 1) * fs if lo < thr_t else None
+                if len(queues[i]) + 2 > cap:
+                    front = None if front is None else front          # never reached with these sizes
+                want_slots.append(RingState.queue_step(queues[i], front, evict, pop, push, begin, n_new, sink * fs))
+            kw = {"host_inputs": inputs} if call % 2 == 0 else {
+                "host_inputs_dev": torch.tensor(inputs, dtype=torch.int64, device=dev)}
+            ops.ring_plan_adaptive(sim.to(dev), thr, qdev, fs, n_new, step, **kw)
+            got = step.cpu()
+            assert got[0].tolist() == inputs[0] and got[2].tolist() == inputs[1] and got[3].tolist() == inputs[2]
+            assert got[1].tolist() == want_slots, (call, got[1].tolist(), want_slots)
+            host = qdev.cpu().tolist()
+            assert [r[1:1 + r[0]] for r in host] == queues, call
+        ops.read_status(dev)
+    # an empty queue in the evict branch is refused (the reference raises there): slot -1 and a status report
+    from streamdiffusionv2_b200 import _native
+    qdev.zero_()
+    ops.ring_plan_adaptive(None, thr, qdev, fs, n_new, step,
+                           host_inputs=[[0] * rows, [0] * rows, [0] * rows, [1] * rows, [1] * rows, [-1] * rows, [0] * rows])
+    assert step[1].tolist() == [-1] * rows
+    with pytest.raises(_native.NativeError, match="out of range"):
+        ops.read_status(dev)

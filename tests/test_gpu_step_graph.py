@@ -66,11 +66,12 @@ def test_indirect_append_refuses_out_of_range_device_parameters(bad):
     ops.read_status(dev)     # the report was cleared
 
 
-def _run_stream(case_name, graphs, swap_at=None, reprompt_at=None):
+def _run_stream(case_name, graphs, swap_at=None, reprompt_at=None, adapt_sink_threshold=-1):
     from model_harness import build_pipeline, snapshot
     case = cases.MODEL_CASES[case_name]
     fs, sched = cases.model_schedule(case)
-    pipe, first, chunks = build_pipeline(case, device="cuda", dtype=torch.bfloat16)
+    pipe, first, chunks = build_pipeline(case, device="cuda", dtype=torch.bfloat16,
+                                         adapt_sink_threshold=adapt_sink_threshold)
     outs = []
     with torch.no_grad():
         torch.manual_seed(11)
@@ -122,3 +123,21 @@ def test_a_new_prompt_mid_stream_is_not_served_from_a_stale_recording():
     for i, (a, b) in enumerate(zip(eager_out, graph_out)):
         assert torch.equal(a, b), f"chunk {i}"
     assert eager_state == graph_state
+
+
+@pytest.mark.parametrize("thr", [0.2, 0.95])
+def test_adaptive_sink_stream_records_and_replays(thr):
+    """The default video-to-video shape (one frame per chunk, sink frames refreshed when the new frame
+    drifts away from them): the data-dependent slot choice runs on the device, so steady steps are
+    recorded and replayed like any other, and leave the outputs, caches, index tensors and evict
+    queues of the launch-by-launch path.  The higher threshold makes the refresh fire often."""
+    from streamdiffusionv2_b200 import ops
+    eager_out, eager_state, _ = _run_stream("m_stream_1f", graphs=False, adapt_sink_threshold=thr)
+    graph_out, graph_state, pipe = _run_stream("m_stream_1f", graphs=True, adapt_sink_threshold=thr)
+    ops.read_status(torch.device("cuda"))
+    assert pipe.step_graphs.replays >= 3, (pipe.step_graphs.replays, pipe.step_graphs.eager_steps)
+    for i, (a, b) in enumerate(zip(eager_out, graph_out)):
+        assert torch.equal(a, b), f"chunk {i}"
+    assert eager_state == graph_state
+    if thr > 0.9:      # refreshed sink slots show up as queue entries inside the sink region at some point
+        assert any(st["evict_idx"] for st in graph_state)
