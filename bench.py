@@ -34,10 +34,12 @@ FRAME_TOKENS = 1560          # 30 x 52 tokens per latent frame at 480 x 832
 LATENT_HW = (60, 104)
 CACHE_FRAMES = 21            # 1 sink + 20 ring
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch at the N=1 workload's shape (ncu, B200)
-ATTN_DRAM_BYTES_1P3B = 450.4e6 + 14.5e6
-APPEND_DRAM_BYTES_1P3B = 57.56e6 + 11.5e6
+ATTN_DRAM_BYTES_1P3B = 448.0e6 + 14.7e6
+APPEND_DRAM_BYTES_1P3B = 57.59e6 + 8.88e6
 FRAMES_PER_CHUNK = 2
 VIDEO_FRAMES_PER_CHUNK = 4 * FRAMES_PER_CHUNK
+SINK_FRAMES = 1
+ADAPT_SINK_THRESHOLD = -1    # > -1: sink frames are refreshed when the new frame drifts away from them
 LEVELS = [700, 500]
 MODEL_1P3B = dict(model_type="t2v", patch_size=(1, 2, 2), text_len=512, in_dim=16, dim=1536, ffn_dim=8960,
                   freq_dim=256, text_dim=4096, out_dim=16, num_heads=12, num_layers=30, qk_norm=True,
@@ -256,8 +258,10 @@ def metric_name():
 
 def workload_config(n_gpus: int):
     name = "Wan-1.3B" if MODEL_1P3B["dim"] == 1536 else "Wan-14B"
+    adaptive = f", adaptive sink refresh below {ADAPT_SINK_THRESHOLD}" if ADAPT_SINK_THRESHOLD > -1 else ""
     return {"workload": f"random-init causal {name} DiT, 480x832, {len(LEVELS)} denoise levels ({len(LEVELS)} cache "
-                        "rows), 2 latent frames per chunk, 1 sink + 20 ring frame cache, full and wrapping",
+                        f"rows), {FRAMES_PER_CHUNK} latent frame(s) per chunk, {SINK_FRAMES} sink + "
+                        f"{CACHE_FRAMES - SINK_FRAMES} ring frame cache, full and wrapping{adaptive}",
             "tokens_per_chunk_row": FRAMES_PER_CHUNK * FRAME_TOKENS, "cache_tokens": CACHE_FRAMES * FRAME_TOKENS,
             "cache_rows": len(LEVELS), "blocks": MODEL_1P3B["num_layers"],
             "parallelism": "single GPU" if n_gpus == 1 else f"pipeline of {n_gpus} contiguous block ranges",
@@ -283,8 +287,8 @@ def build_pipeline(device, n_layers_override=None):
     g = torch.Generator(device="cpu").manual_seed(1)
     prompt = torch.randn(1, 512, kw["text_dim"], generator=g).to(device=device, dtype=torch.bfloat16)
     pipe = StreamPipeline(DiffusionWrapper(model), lambda text_prompts: {"prompt_embeds": prompt.clone()}, LEVELS,
-                          kw["num_layers"], kw["num_heads"], FRAME_TOKENS, CACHE_FRAMES, 1, -1, FRAMES_PER_CHUNK,
-                          device=device)
+                          kw["num_layers"], kw["num_heads"], FRAME_TOKENS, CACHE_FRAMES, SINK_FRAMES, ADAPT_SINK_THRESHOLD,
+                          FRAMES_PER_CHUNK, device=device)
     return pipe
 
 
@@ -292,7 +296,8 @@ class ChunkSchedule:
     """Chunk starts as the reference's drivers advance them, with the refresh rule
     (streamv2v/inference.py:234-252).  The first chunk (`first_frames`) was taken by prepare()."""
 
-    def __init__(self, first_frames=1 + FRAMES_PER_CHUNK):
+    def __init__(self, first_frames=None):
+        first_frames = 1 + FRAMES_PER_CHUNK if first_frames is None else first_frames
         self.start = FRAME_TOKENS * first_frames
         self.end = self.start + FRAMES_PER_CHUNK * FRAME_TOKENS
 
@@ -426,9 +431,10 @@ def reference_gpu_arms(device, steps, warmup, dev_chunks, first):
                     out[label] = {"unavailable": "flash-attn does not import on this box"}
                     return
                 torch.manual_seed(0)
-                pipe = build_reference_pipeline(ref, MODEL_1P3B, LEVELS, FRAME_TOKENS, CACHE_FRAMES, 1,
+                pipe = build_reference_pipeline(ref, MODEL_1P3B, LEVELS, FRAME_TOKENS, CACHE_FRAMES, SINK_FRAMES,
                                                 FRAMES_PER_CHUNK, prompt, device=device, dtype=torch.bfloat16,
                                                 init_parameters=init, construct_on_device=True)
+                pipe.adapt_sink_threshold = ADAPT_SINK_THRESHOLD
                 if patch:
                     from streamdiffusionv2_b200.causal_attention import install
                     install(pipe.generator.model)
@@ -617,21 +623,26 @@ def run_single_gpu(args):
         "gpu_launches": launches, "gpu_launches_by_kernel": log.counts,
         "roofline": {"kernel": "attn_kvcache (tcgen05)", "bound": "tensor", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
-                     "traffic": ATTN_DRAM_BYTES_1P3B if MODEL_1P3B["dim"] == 1536 else None,
+                     "traffic": ATTN_DRAM_BYTES_1P3B if MODEL_1P3B["dim"] == 1536 and CACHE_FRAMES == 21 else None,
                      "traffic_note": "DRAM bytes read + written per launch, one ncu capture of this shape "
                                      "(2 rows x 12 heads x 3120 queries x 32760 keys); algorithmic K+V+Q+out = 441 MB",
                      "avg_launch_ms": att_ms, "flops_per_launch": att_flops,
                      "share_of_step": att_ms * log.counts["attn_kvcache"] / regions[0],
                      "timed_in": "launch-by-launch pass of the same steps after the timed region (graph replay "
                                  "hides single launches from events)" if args.graphs else "the timed region"},
-        "roofline_append": {"kernel": "rope_kv_append", "bound": "hbm", "achieved": app_bytes / (app_ms * 1e-3) / 1e9,
+        "roofline_append": {"kernel": "rope_kv_append with the q/k RMS norm folded in (one launch where the unfused "
+                                      "block ran the append and two norm launches: 192 MB of traffic instead of 115 MB)",
+                            "bound": "hbm", "achieved": app_bytes / (app_ms * 1e-3) / 1e9,
                             "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": app_bytes / (app_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                             "avg_launch_ms": app_ms, "bytes_per_launch": app_bytes,
-                            "traffic": APPEND_DRAM_BYTES_1P3B if MODEL_1P3B["dim"] == 1536 else None,
+                            "traffic": APPEND_DRAM_BYTES_1P3B if MODEL_1P3B["dim"] == 1536 and FRAMES_PER_CHUNK == 2 else None,
                             "traffic_note": "DRAM bytes per launch, one ncu capture of this shape from a flushed "
-                                            "cache: all 57.5 MB of reads, 11.5 MB of the 57.5 MB of writes (the "
-                                            "rest is still in L2 when the kernel ends)"},
+                                            "cache: all 57.5 MB of reads, 8.9 MB of the 57.5 MB of writes (the "
+                                            "rest is still in L2 when the kernel ends); with the norm the launch is "
+                                            "bound by the f32<->f64 conversion unit (64 % busy), not by HBM; the "
+                                            "plain append kernel reaches 0.59 of the HBM peak at this shape and 0.85 "
+                                            "at 4 rows x 40 heads (kernel_bench.py)"},
         "cross_attn": {"avg_launch_ms": statistics.mean(crs) if crs else None,
                        "tflops": (tlog.work["cross_attn"] / tlog.counts["cross_attn"]) / (statistics.mean(crs) * 1e-3) / 1e12
                        if crs else None},
@@ -907,12 +918,20 @@ def main():
                          "one region there, then re-plan the ranges from measured per-half-block costs (stage "
                          "boundaries may fall inside a block) and move the blocks; measured-blocks = the same with "
                          "boundaries at whole blocks")
+    ap.add_argument("--workload", default="config2", choices=["config2", "v2v-default"],
+                    help="config2: the headline workload (2 frames per chunk, 1 sink + 20 ring frames); v2v-default: the "
+                         "reference's default video-to-video configuration (configs/wan_causal_dmd_v2v.yaml:53-56: 1 "
+                         "frame per chunk, 6-frame cache, 3 sink frames refreshed adaptively below 0.2), N=1 only")
     ap.add_argument("--model", default="1.3b", choices=["1.3b", "14b"],
                     help="1.3b is the headline workload; 14b = 40 blocks, dim 5120, 40 heads, 4 denoise levels")
     args = ap.parse_args()
     if args.model == "14b":
         MODEL_1P3B.update(dim=5120, ffn_dim=13824, num_heads=40, num_layers=40)
         LEVELS[:] = [1000, 750, 500, 250]
+    if args.workload == "v2v-default":
+        global FRAMES_PER_CHUNK, VIDEO_FRAMES_PER_CHUNK, CACHE_FRAMES, SINK_FRAMES, ADAPT_SINK_THRESHOLD
+        FRAMES_PER_CHUNK, VIDEO_FRAMES_PER_CHUNK, CACHE_FRAMES, SINK_FRAMES, ADAPT_SINK_THRESHOLD = 1, 4, 6, 3, 0.2
+        args.no_cpu_baseline = True
     args.warmup = max(args.warmup, 0)
     # Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line
     # there, so everything but that line goes to stderr.

@@ -126,3 +126,75 @@ def test_install_on_reference_classes_bf16_against_the_reference_gpu_path(name, 
         scale = b.abs().mean().item()
         assert err.mean().item() <= 0.03 * scale and err.max().item() <= 0.5 * b.abs().max().item(), \
             (i, err.mean().item(), err.max().item(), scale)
+
+
+# ------------------------------------------------------------------------------------------------
+# one layer, teacher-forced: the reference's own module on the GPU beside the kernels
+# ------------------------------------------------------------------------------------------------
+@needs_reference
+@pytest.mark.parametrize("name", ["k_bf16_stream", "k_bf16_single_2level", "k_bf16_1frame_sink3", "k_bf16_sink0_3frames"])
+def test_layer_against_the_reference_module_on_the_gpu(name):
+    """The reference's CausalWanSelfAttention on the GPU in bf16 (its stock path: fp64 complex rope on
+    the device, slice writes, flash_attn_with_kvcache) and the kernels are fed the same projected
+    q/k/v call after call, each against its own cache.  Index tensors, evict queues and step counters
+    must be identical after every call; the caches equal - bit for bit, except where the device's
+    fused multiply-add in the reference's complex product rounds the last place the other way
+    (allowed: at most 1e-5 of the elements, one bf16 step) - and the outputs equal to the attention
+    tolerance, against flash-attn itself."""
+    import make_golden
+    import replay
+    from streamdiffusionv2_b200 import causal_attention as ca
+    ref = import_reference(REFERENCE, flash_attn=True)
+    try:
+        case = cases.KERNEL_CASES[name]
+        H, D = case["heads"], case["head_dim"]
+        dtype, dev = torch.bfloat16, torch.device("cuda")
+        h, w = case["grid_hw"]
+        fs = h * w
+        smax = case["cache_frames"] * fs
+        layer = make_golden.make_ref_layer(ref, H, D, case["sink_size"], case["adapt_sink_thr"]).to(dev)
+        table = make_golden.ref_table(ref, D).to(dev)
+        mk = lambda: {"k": torch.zeros(1, smax, H, D, dtype=dtype, device=dev),
+                      "v": torch.zeros(1, smax, H, D, dtype=dtype, device=dev),
+                      "global_end_index": torch.tensor([0], dtype=torch.long, device=dev),
+                      "local_end_index": torch.tensor([0], dtype=torch.long, device=dev),
+                      "total_steps": case["total_steps"], "current_step": case["total_steps"]}
+        kv_ref, kv = mk(), mk()
+        mod = replay._AttnState(H, D, case["sink_size"], case["adapt_sink_thr"])
+        freqs = make_golden.ref_table(ref, D)            # complex128 on the host: the table both sides were built from
+        gen = cases.InputStream(case)
+        n_calls = 0
+        for call in cases.schedule(case):
+            if call["op"] == "replicate":
+                for c in (kv_ref, kv):
+                    b = call["rows"]
+                    c["k"], c["v"] = c["k"].repeat(b, 1, 1, 1), c["v"].repeat(b, 1, 1, 1)
+                    c["global_end_index"] = c["global_end_index"].repeat(b)
+                    c["local_end_index"] = c["local_end_index"].repeat(b)
+                continue
+            starts, frames = call["starts"], call["frames"]
+            q, k, v = (t.to(dev) for t in gen.next(len(starts), frames * fs))
+            layer.q.value, layer.k.value, layer.v.value = (t.flatten(2) for t in (q, k, v))
+            grid = torch.tensor([[frames, h, w]] * len(starts), dtype=torch.long)
+            cs = torch.tensor(starts, dtype=torch.long, device=dev)
+            x = torch.zeros(len(starts), frames * fs, H * D, dtype=dtype, device=dev)
+            with torch.no_grad():
+                want = layer(x, None, grid, table, None, kv_ref, cs, cs + frames * fs).view(len(starts), -1, H, D)
+            got = ca.cached_attention(mod, q, k, v, grid, freqs, kv, cs)
+            assert kv["global_end_index"].tolist() == kv_ref["global_end_index"].tolist(), (name, n_calls)
+            assert kv["local_end_index"].tolist() == kv_ref["local_end_index"].tolist(), (name, n_calls)
+            assert mod.evict_idx == [list(map(int, r)) for r in layer.evict_idx], (name, n_calls)
+            assert kv["current_step"] == kv_ref["current_step"], (name, n_calls)
+            assert torch.equal(kv["v"], kv_ref["v"]), (name, n_calls)
+            diff = kv["k"].view(torch.int16) != kv_ref["k"].view(torch.int16)
+            if diff.any():
+                assert diff.float().mean().item() <= 1e-5, (name, n_calls, diff.float().mean().item())
+                a, b = kv["k"][diff].float(), kv_ref["k"][diff].float()
+                assert ((a - b).abs() <= b.abs() * 2.0 ** -7).all(), (name, n_calls)
+                kv["k"].copy_(kv_ref["k"])           # teacher forcing: the next call starts from the reference's cache
+            err = (got.float() - want.float()).abs()
+            assert err.max().item() <= 2e-2 and err.mean().item() <= 1e-3, (name, n_calls, err.max().item())
+            n_calls += 1
+        assert n_calls > 8
+    finally:
+        set_flash_attn(ref, False)
