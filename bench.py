@@ -905,7 +905,7 @@ def main():
     ap.add_argument("--no-reference-gpu", action="store_true",
                     help="N=1: skip the reference's GPU path (timed in the same process after this package's own)")
     ap.add_argument("--reference-steps", type=int, default=6, help="timed chunk steps per reference GPU arm")
-    ap.add_argument("--cpu-budget", type=float, default=150.0, help="--impl reference: seconds of CPU work")
+    ap.add_argument("--cpu-budget", type=float, default=90.0, help="--impl reference: seconds of CPU work")
     ap.add_argument("--min-seconds", type=float, default=2.0,
                     help="the timed region of K steps is repeated until the regions cover this long; median counts")
     ap.add_argument("--max-repeats", type=int, default=8)

@@ -145,6 +145,22 @@ int sdv2_norm_rope_kv_append(const sdv2_view* q, const sdv2_view* k, const sdv2_
                              int* status_dev, void* stream);
 
 /*
+ * Per-frame means for the adaptive sink test: for every cache row, the mean over the tokens of each of
+ * the first sink_frames frames of the K and V cache and of the new frame's roped K and V
+ * (k_new / v_new: [rows, frame_tokens, heads, head_dim]) - the four `.mean(1)` reductions of
+ * models/wan/causal_model.py:286-293 for all rows in two launches, without the reshaped copies.
+ * means_dev: out, [rows][sink_frames + 1][2 (K, V)][heads * head_dim] in the tensors' type (fp32 sums,
+ * scaled by 1 / frame_tokens, rounded once); entry sink_frames is the new frame.
+ * scratch_dev: at least sdv2_frame_means_scratch_bytes() bytes, 16-byte aligned, no initialisation needed.
+ * The heads of a token must be back to back (stride_head == head_dim).
+ */
+int sdv2_frame_means(const sdv2_view* k_cache, const sdv2_view* v_cache, const sdv2_view* k_new,
+                     const sdv2_view* v_new, int rows, int sink_frames, int frame_tokens, int heads, int head_dim,
+                     int64_t cache_tokens, int dtype, void* means_dev, void* scratch_dev, size_t scratch_bytes,
+                     void* stream);
+size_t sdv2_frame_means_scratch_bytes(int rows, int sink_frames, int heads, int head_dim);
+
+/*
  * Data-dependent half of the sink + ring slot logic, on the device, for the adaptive sink refresh
  * (models/wan/causal_model.py:284-299 for the test, :302-337 for the queue): one launch per layer
  * decides for every cache row whether a sink frame is refreshed, updates the row's evict queue and

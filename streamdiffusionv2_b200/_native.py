@@ -51,6 +51,9 @@ _SIGNATURES = {
                                                                     C.POINTER(C.c_int64), C.POINTER(C.c_int64),
                                                                     C.c_void_p, C.c_void_p, C.c_float,
                                                                     C.c_void_p, C.c_void_p]),
+    "sdv2_frame_means": (C.c_int, [C.POINTER(View)] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64,
+                                                            C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sdv2_frame_means_scratch_bytes": (C.c_size_t, [C.c_int] * 4),
     "sdv2_ring_plan_adaptive": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_int,
                                           C.c_int64, C.c_int64, C.POINTER(C.c_int64), C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_void_p]),

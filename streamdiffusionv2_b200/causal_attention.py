@@ -81,11 +81,17 @@ def adaptive_similarities(kv_cache, roped_k, v, sink_size: int, frame_tokens: in
     the same for V, averaged.  Rows are independent (row i reads cache row i only).  Stays on the
     device: the threshold test and everything that follows from it run in the plan kernel."""
     rows = roped_k.shape[0]
-    sink_tokens = sink_size * frame_tokens
-    k_sink = kv_cache["k"][:rows, :sink_tokens].reshape(rows, sink_size, frame_tokens, -1).mean(2)
-    k_new = roped_k.reshape(rows, 1, frame_tokens, -1).mean(2)
-    v_sink = kv_cache["v"][:rows, :sink_tokens].reshape(rows, sink_size, frame_tokens, -1).mean(2)
-    v_new = v.reshape(rows, 1, frame_tokens, -1).mean(2)
+    if roped_k.is_cuda:
+        # the four means in two launches, straight from the cache (no reshaped copies)
+        means = ops.frame_means(kv_cache["k"][:rows], kv_cache["v"][:rows], roped_k, v, sink_size, frame_tokens)
+        k_sink, k_new = means[:, :sink_size, 0], means[:, sink_size:, 0]
+        v_sink, v_new = means[:, :sink_size, 1], means[:, sink_size:, 1]
+    else:                                      # host tensors: only the tests of the host logic come here
+        sink_tokens = sink_size * frame_tokens
+        k_sink = kv_cache["k"][:rows, :sink_tokens].reshape(rows, sink_size, frame_tokens, -1).mean(2)
+        k_new = roped_k.reshape(rows, 1, frame_tokens, -1).mean(2)
+        v_sink = kv_cache["v"][:rows, :sink_tokens].reshape(rows, sink_size, frame_tokens, -1).mean(2)
+        v_new = v.reshape(rows, 1, frame_tokens, -1).mean(2)
     k_sim = torch.cosine_similarity(k_sink, k_new, dim=-1)
     v_sim = torch.cosine_similarity(v_sink, v_new, dim=-1)
     return ((k_sim + v_sim) / 2).contiguous()

@@ -386,6 +386,40 @@ int sdv2_selftest_umma(const void* a_dev, const void* b_dev, const void* p_dev, 
   return e == cudaSuccess ? SDV2_OK : cuda_fail(e);
 }
 
+size_t sdv2_frame_means_scratch_bytes(int rows, int sink_frames, int heads, int head_dim) {
+  if (rows <= 0 || sink_frames < 0 || heads <= 0 || head_dim <= 0) return 0;
+  return static_cast<size_t>(rows) * (sink_frames + 1) * 2 * sdv2::kFrameMeanChunks * heads * head_dim * sizeof(float);
+}
+
+int sdv2_frame_means(const sdv2_view* k_cache, const sdv2_view* v_cache, const sdv2_view* k_new, const sdv2_view* v_new,
+                     int rows, int sink_frames, int frame_tokens, int heads, int head_dim, int64_t cache_tokens,
+                     int dtype, void* means_dev, void* scratch_dev, size_t scratch_bytes, void* stream) {
+  if (rows <= 0 || sink_frames < 0 || frame_tokens <= 0 || heads <= 0 || head_dim <= 0) return SDV2_ERR_INVALID_ARG;
+  if (dtype != SDV2_DTYPE_BF16 && dtype != SDV2_DTYPE_F32) return SDV2_ERR_INVALID_ARG;
+  if (rows > SDV2_MAX_ROWS || sink_frames > 64) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  if (static_cast<int64_t>(sink_frames) * frame_tokens > cache_tokens) return SDV2_ERR_INVALID_ARG;
+  if (means_dev == nullptr || scratch_dev == nullptr) return SDV2_ERR_INVALID_ARG;
+  if (scratch_bytes < sdv2_frame_means_scratch_bytes(rows, sink_frames, heads, head_dim)) return SDV2_ERR_WORKSPACE;
+  const int esize = dtype == SDV2_DTYPE_BF16 ? 2 : 4;
+  if ((heads * head_dim) % (16 / esize)) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  if (!aligned16(means_dev) || !aligned16(scratch_dev)) return SDV2_ERR_MISALIGNED;
+  int rc;
+  const sdv2_view* views[4] = {k_cache, v_cache, k_new, v_new};
+  for (const sdv2_view* vw : views) {
+    if ((rc = check_view(vw, esize, false)) != SDV2_OK) return rc;
+    if (vw->stride_head != head_dim) return SDV2_ERR_UNSUPPORTED_SHAPE;   // a token's heads as one run
+  }
+  sdv2::FrameMeansParams p;
+  memset(&p, 0, sizeof(p));
+  p.k_cache = *k_cache; p.v_cache = *v_cache; p.k_new = *k_new; p.v_new = *v_new;
+  p.rows = rows; p.sink_frames = sink_frames; p.frame_tokens = frame_tokens; p.row_elems = heads * head_dim;
+  p.dtype = dtype; p.chunks = sdv2::kFrameMeanChunks;
+  p.partial = static_cast<float*>(scratch_dev);
+  p.means = means_dev;
+  cudaError_t e = sdv2::launch_frame_means(p, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? SDV2_OK : cuda_fail(e);
+}
+
 int sdv2_ring_plan_adaptive(const void* sim_dev, int sim_dtype, int rows, int sink_frames, float threshold,
                             int64_t* queue_dev, int queue_cap, int64_t frame_tokens, int64_t new_tokens,
                             const int64_t* host_inputs, const int64_t* host_inputs_dev, int64_t* step_params_dev,

@@ -102,6 +102,77 @@ __global__ void __launch_bounds__(64) ring_plan_kernel(const __grid_constant__ R
   p.step_params[3 * p.rows + row] = local_end;
 }
 
+// ------------------------------------------------------------------------------------------
+// per-frame means of K and V for the adaptive test: every sink frame of the cache and the new frame
+// ------------------------------------------------------------------------------------------
+// Pass 1: grid (token chunks, (sink + 1) frames x 2 tensors, rows); a thread owns 16-byte vectors of
+// the token row and sums them over its chunk of the frame's tokens in fp32.  Pass 2 adds the chunk
+// partials in chunk order (so the result does not depend on scheduling), scales by 1 / tokens and
+// rounds to the tensors' type - what a mean over the token dimension of a [frames, tokens, C] tensor
+// gives up to the order of the fp32 additions.
+template <typename T>
+__global__ void __launch_bounds__(256) frame_sum_kernel(const __grid_constant__ FrameMeansParams p) {
+  constexpr int kElems = 16 / sizeof(T);
+  const int chunk = blockIdx.x, row = blockIdx.z;
+  const int frame = blockIdx.y >> 1, tensor = blockIdx.y & 1;   // frame == sink_frames: the new frame
+  const bool is_new = frame == p.sink_frames;
+  const sdv2_view& vw = is_new ? (tensor ? p.v_new : p.k_new) : (tensor ? p.v_cache : p.k_cache);
+  const int t0 = static_cast<int>(static_cast<int64_t>(chunk) * p.frame_tokens / gridDim.x);
+  const int t1 = static_cast<int>(static_cast<int64_t>(chunk + 1) * p.frame_tokens / gridDim.x);
+  const int64_t tok0 = is_new ? 0 : static_cast<int64_t>(frame) * p.frame_tokens;
+  const T* base = static_cast<const T*>(vw.ptr) + row * vw.stride_row + tok0 * vw.stride_tok;
+  const int row_vecs = p.row_elems / kElems;
+  float* out = p.partial + ((static_cast<size_t>(row) * (p.sink_frames + 1) + frame) * 2 + tensor) * gridDim.x * p.row_elems +
+               static_cast<size_t>(chunk) * p.row_elems;
+  for (int c = threadIdx.x; c < row_vecs; c += blockDim.x) {
+    float acc[kElems];
+#pragma unroll
+    for (int i = 0; i < kElems; ++i) acc[i] = 0.f;
+    for (int t = t0; t < t1; ++t) {
+      const uint4 v = *reinterpret_cast<const uint4*>(base + t * vw.stride_tok + c * kElems);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      if (sizeof(T) == 2) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] += __uint_as_float(w[i] << 16);
+          acc[2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] += __uint_as_float(w[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kElems; ++i) out[c * kElems + i] = acc[i];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) frame_mean_kernel(const __grid_constant__ FrameMeansParams p) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= p.row_elems) return;
+  const size_t item = (static_cast<size_t>(blockIdx.z) * (p.sink_frames + 1) + (blockIdx.y >> 1)) * 2 + (blockIdx.y & 1);
+  const float* part = p.partial + item * p.chunks * p.row_elems + e;
+  float s = 0.f;
+  for (int c = 0; c < p.chunks; ++c) s += part[static_cast<size_t>(c) * p.row_elems];
+  const float m = s * (1.0f / static_cast<float>(p.frame_tokens));
+  T* out = static_cast<T*>(p.means) + item * p.row_elems + e;
+  if (sizeof(T) == 2) *reinterpret_cast<__nv_bfloat16*>(out) = __float2bfloat16_rn(m);
+  else *reinterpret_cast<float*>(out) = m;
+}
+
+cudaError_t launch_frame_means(const FrameMeansParams& p, cudaStream_t stream) {
+  const dim3 g1(p.chunks, (p.sink_frames + 1) * 2, p.rows), g2((p.row_elems + 255) / 256, (p.sink_frames + 1) * 2, p.rows);
+  if (p.dtype == SDV2_DTYPE_BF16) {
+    frame_sum_kernel<__nv_bfloat16><<<g1, 256, 0, stream>>>(p);
+    frame_mean_kernel<__nv_bfloat16><<<g2, 256, 0, stream>>>(p);
+  } else {
+    frame_sum_kernel<float><<<g1, 256, 0, stream>>>(p);
+    frame_mean_kernel<float><<<g2, 256, 0, stream>>>(p);
+  }
+  return cudaGetLastError();
+}
+
 cudaError_t launch_ring_plan(const RingPlanParams& p, cudaStream_t stream) {
   ring_plan_kernel<<<1, 64, 0, stream>>>(p);
   return cudaGetLastError();

@@ -178,6 +178,15 @@ struct RingPlanParams {
 };
 cudaError_t launch_ring_plan(const RingPlanParams& p, cudaStream_t stream);
 
+constexpr int kFrameMeanChunks = 16;   // token chunks per frame in the first pass
+struct FrameMeansParams {
+  sdv2_view k_cache, v_cache, k_new, v_new;   // heads of a token back to back
+  int rows, sink_frames, frame_tokens, row_elems, dtype, chunks;
+  float* partial;   // [rows][sink + 1][2][chunks][row_elems]
+  void* means;      // [rows][sink + 1][2][row_elems], in the tensors' type
+};
+cudaError_t launch_frame_means(const FrameMeansParams& p, cudaStream_t stream);
+
 cudaError_t launch_wait_timeout_selftest(int* status, long long budget_cycles, cudaStream_t stream);
 
 }  // namespace sdv2

@@ -170,6 +170,29 @@ def rope_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: t
     return q_out
 
 
+_mean_scratch: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def frame_means(k_cache: torch.Tensor, v_cache: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                sink_frames: int, frame_tokens: int) -> torch.Tensor:
+    """[rows, sink_frames + 1, 2, H * D] per-frame means (K, V) of the cache's sink frames and of the new
+    frame (last entry), in the tensors' dtype, for the adaptive sink test."""
+    rows, _, H, D = k_new.shape
+    means = torch.empty((rows, sink_frames + 1, 2, H * D), dtype=k_new.dtype, device=k_new.device)
+    need = int(N.lib().sdv2_frame_means_scratch_bytes(rows, sink_frames, H, D))
+    idx = k_new.device.index if k_new.device.index is not None else torch.cuda.current_device()
+    scratch = _mean_scratch.get((idx, need))
+    if scratch is None:
+        scratch = _mean_scratch[(idx, need)] = torch.empty(need, dtype=torch.uint8, device=k_new.device)
+    views = [N.view(t) for t in (k_cache, v_cache, k_new, v_new)]
+    with _Logged("frame_means", 2.0 * rows * (sink_frames + 1) * frame_tokens * H * D * k_new.element_size()):
+        rc = N.lib().sdv2_frame_means(*[C.byref(x) for x in views], rows, sink_frames, frame_tokens, H, D,
+                                      k_cache.shape[1], N.dtype_code(k_new.dtype), means.data_ptr(),
+                                      scratch.data_ptr(), scratch.numel(), N.stream_ptr(k_new.device))
+    N.check(rc, "sdv2_frame_means")
+    return means
+
+
 def ring_plan_adaptive(sim: Optional[torch.Tensor], threshold: float, queue: torch.Tensor, frame_tokens: int,
                        n_new: int, step_params: torch.Tensor, *, host_inputs: Optional[Sequence[Sequence[int]]] = None,
                        host_inputs_dev: Optional[torch.Tensor] = None) -> None:

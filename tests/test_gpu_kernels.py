@@ -513,3 +513,34 @@ def test_device_plan_kernel_follows_the_host_statement_of_the_queue_logic():
     assert step[1].tolist() == [-1] * rows
     with pytest.raises(_native.NativeError, match="out of range"):
         ops.read_status(dev)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_frame_means_match_the_reference_reductions(dtype):
+    """The per-frame means the adaptive sink test needs (sink frames of the K / V cache, the new
+    frame), two launches for all rows, against the `.mean` reductions of the reference's op chain:
+    same fp32 sums up to the order of the additions, rounded once to the tensors' type."""
+    ops = _ops()
+    rows, sink, fs, H, D, S = 3, 3, 1560, 12, 128, 9 * 1560
+    g = torch.Generator().manual_seed(17)
+    kc = (torch.randn(rows, S, H, D, generator=g) + 0.3).to(dtype).cuda()
+    vc = (torch.randn(rows, S, H, D, generator=g) - 0.2).to(dtype).cuda()
+    kn = (torch.randn(rows, fs, H, D, generator=g) + 0.1).to(dtype).cuda()
+    vn = torch.randn(rows, fs, H, D, generator=g).to(dtype).cuda()
+    means = ops.frame_means(kc, vc, kn, vn, sink, fs)
+    assert means.shape == (rows, sink + 1, 2, H * D) and means.dtype == dtype
+    for tensor, cache, new in ((0, kc, kn), (1, vc, vn)):
+        want_sink = cache[:, :sink * fs].reshape(rows, sink, fs, -1).mean(2)
+        want_new = new.reshape(rows, 1, fs, -1).mean(2)
+        for got, want in ((means[:, :sink, tensor], want_sink), (means[:, sink:, tensor], want_new)):
+            if dtype == torch.float32:
+                assert torch.allclose(got, want, rtol=0, atol=2e-6)
+            else:
+                assert (got == want).float().mean().item() > 0.995
+                assert ((got.float() - want.float()).abs() <= want.float().abs() * 2.0 ** -7 + 1e-9).all()
+    # a cache that is a slice of a larger buffer (row stride != tokens x row) works too
+    big = torch.zeros(rows, S + 50, H, D, dtype=dtype, device="cuda")
+    big[:, :S] = kc
+    m2 = ops.frame_means(big[:, :S], vc, kn, vn, sink, fs)
+    assert torch.equal(m2, means)
+    ops.read_status(torch.device("cuda"))

@@ -147,3 +147,31 @@ def test_device_status_surfaces_from_the_streaming_entry_points(monkeypatch):
         with pytest.raises(_native.NativeError, match="status"):
             pipe.inference(noise=chunks[2], current_start=sched[2][0], current_end=sched[2][1], current_step=None,
                            block_mode="input", block_num=[0, 2])
+
+
+def test_concatenated_qkv_weight_follows_the_parameters():
+    """The q|k|v projection runs as one GEMM over a concatenated copy of the three weights; the copy is
+    rebuilt whenever a parameter is written (load_state_dict, in-place updates) or replaced, and the
+    parameters themselves keep their names and values."""
+    from streamdiffusionv2_b200.causal_attention import _fused_qkv_weights
+    from streamdiffusionv2_b200.wan_model import CausalSelfAttention
+    torch.manual_seed(0)
+    attn = CausalSelfAttention(256, 2)
+    names = sorted(n for n, _ in attn.named_parameters())
+    w, b = _fused_qkv_weights(attn)
+    assert w.shape == (768, 256) and b.shape == (768,)
+    assert torch.equal(w[256:512], attn.k.weight) and torch.equal(b[512:], attn.v.bias)
+    assert _fused_qkv_weights(attn)[0] is w                                  # cached while nothing changes
+    x = torch.randn(3, 5, 256)
+    q, k, v = torch.nn.functional.linear(x, w, b).view(3, 5, 3, 256).unbind(2)
+    assert torch.allclose(q, attn.q(x), atol=1e-5) and torch.allclose(v, attn.v(x), atol=1e-5)
+    state = {n: torch.randn_like(p) for n, p in attn.state_dict().items()}
+    attn.load_state_dict(state, strict=True)                                  # copies in place: version counters move
+    w2, b2 = _fused_qkv_weights(attn)
+    assert w2 is not w and torch.equal(w2[:256], state["q.weight"]) and torch.equal(b2[256:512], state["k.bias"])
+    with torch.no_grad():
+        attn.v.weight.mul_(2.0)
+    assert torch.equal(_fused_qkv_weights(attn)[0][512:], attn.v.weight)
+    attn.q.weight = torch.nn.Parameter(torch.zeros(256, 256))                 # replaced outright
+    assert float(_fused_qkv_weights(attn)[0][:256].abs().max()) == 0.0
+    assert sorted(n for n, _ in attn.named_parameters()) == names            # nothing was registered on the module
