@@ -85,9 +85,11 @@ def balanced_block_ranges(total_blocks: int, world_size: int) -> List[List[int]]
     return out
 
 
-def partition_by_cost(costs: Sequence[float], overheads: Sequence[float], boundary_step: int = 1) -> List[List[int]]:
+def partition_by_cost(costs: Sequence[float], overheads: Sequence[float], boundary_step: int = 1,
+                      scales: Optional[Sequence[float]] = None) -> List[List[int]]:
     """Contiguous, non-empty ranges of `costs` (one per stage, in order) that minimise the slowest
-    stage's time max_r(overheads[r] + sum of the costs in range r): the run-time counterpart of the
+    stage's time max_r(overheads[r] + scales[r] * sum of the costs in range r) - `scales` (default 1)
+    lets stages differ in speed, which GPUs under a power cap do by several per cent: the run-time counterpart of the
     reference's compute_balanced_split (streamv2v/communication/utils.py:141-229), which moves
     whole blocks proportionally to the measured imbalance; this one takes the measured cost of
     every unit and the fixed extra time of every stage (patch embedding and row shift on the
@@ -97,6 +99,9 @@ def partition_by_cost(costs: Sequence[float], overheads: Sequence[float], bounda
     n, w = len(costs), len(overheads)
     if w < 1 or n < w * boundary_step:
         raise ValueError("fewer units than stages")
+    scales = [1.0] * w if scales is None else [float(x) for x in scales]
+    if len(scales) != w or min(scales) <= 0:
+        raise ValueError("one positive scale per stage")
     prefix = [0.0]
     for c in costs:
         prefix.append(prefix[-1] + float(c))
@@ -108,11 +113,11 @@ def partition_by_cost(costs: Sequence[float], overheads: Sequence[float], bounda
     best = [[inf] * len(cuts) for _ in range(w)]
     back = [[-1] * len(cuts) for _ in range(w)]
     for j in range(1, len(cuts)):
-        best[0][j] = overheads[0] + prefix[cuts[j]]
+        best[0][j] = overheads[0] + scales[0] * prefix[cuts[j]]
     for r in range(1, w):
         for j in range(r + 1, len(cuts)):
             for i in range(r, j):
-                t = max(best[r - 1][i], overheads[r] + prefix[cuts[j]] - prefix[cuts[i]])
+                t = max(best[r - 1][i], overheads[r] + scales[r] * (prefix[cuts[j]] - prefix[cuts[i]]))
                 if t < best[r][j]:
                     best[r][j], back[r][j] = t, i
     out, j = [], len(cuts) - 1

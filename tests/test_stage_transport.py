@@ -72,7 +72,8 @@ def _worker_pipeline(rank, world, port, ranges, quiesce_every, q, park_at=(), ha
                     last = True
                 if replan_at is not None and i == replan_at[1]:
                     # measured steps are over and the ring was emptied: plan from the gathered costs and move
-                    planned = runner.plan_ranges(replan_at[2])
+                    planned = runner.plan_ranges(replan_at[2],
+                                                 stage_ms=replan_at[3][rank] if len(replan_at) > 3 else None)
                     runner.rebalance(planned, halves=True)
                 o = runner.step(i, noise, cs, ce, None, last=last)
                 if o is not None:
@@ -436,8 +437,35 @@ def test_partition_by_cost_is_optimal_and_respects_block_boundaries():
     three = [1.0, 1.0] * 3
     assert t(partition_by_cost(three, [0, 0], 2), three, [0, 0]) == pytest.approx(4.0)
     assert t(partition_by_cost(three, [0, 0], 1), three, [0, 0]) == pytest.approx(3.0)
+    # stages of different speed (GPUs under a power cap differ by several per cent): the faster ones get more
+    units, scales = [0.725, 0.275] * 30, [1.774, 1.772, 1.663, 1.629]
+    plan = partition_by_cost(units, [0.27, 0, 0, 0.39], boundary_step=2, scales=scales)
+    assert [(b - a) // 2 for a, b in plan] == [7, 7, 8, 8]
+    brute = min(max(o + sc * sum(units[a:b]) for o, sc, (a, b) in zip([0.27, 0, 0, 0.39], scales, zip((0,) + cut, cut + (60,))))
+                for cut in itertools.combinations(range(2, 60, 2), 3))
+    assert abs(t(plan, units, [0, 0, 0, 0]) * 0 + max(o + sc * sum(units[a:b]) for o, sc, (a, b) in
+                                                      zip([0.27, 0, 0, 0.39], scales, plan)) - brute) < 1e-12
     with pytest.raises(ValueError):
         partition_by_cost([1.0], [0.0, 0.0])
+
+
+def test_plan_follows_the_stage_speeds_seen_in_normal_operation():
+    """With each stage's normal-operation time supplied, the launch-by-launch measurements only set
+    proportions and the speeds decide: a stage that is three times slower per block ends up with
+    fewer half blocks; the plan is the same on both ranks and the stream is unchanged by the move."""
+    case = cases.MODEL_CASES["m_stages"]
+    _, z = cases.load_fixture("m_stages")
+    nblk, split = cases.MODEL_KW["num_layers"], case["split"]
+    res = _run(_worker_pipeline, 2, [[0, split], [split, nblk]], 0, {"replan_at": (1, 4, "half", (10.0, 45.0))})
+    for r, v in res.items():
+        assert v[0] == "ok", v[1]
+    info = [next(s for s in res[r][2] if "planned" in s) for r in (0, 1)]
+    assert info[0]["planned"] == info[1]["planned"]
+    (a0, b0), (a1, b1) = info[0]["planned"]
+    assert (a0, b1) == (0, 2 * nblk) and b0 == a1 and b0 - a0 > b1 - a1        # the fast stage took more
+    assert info[0]["costs"]["ms_per_block"][1] > 2 * info[0]["costs"]["ms_per_block"][0]
+    for i, o in enumerate(res[1][1]):
+        assert np.abs(o - z[f"out_{i}"]).max() < 5e-4, i
 
 
 def test_measured_costs_give_every_rank_the_same_plan_and_the_stream_survives_the_move():
