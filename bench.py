@@ -770,8 +770,7 @@ def run_pipeline(args):
             # rank r is r chunks behind rank 0 here; r extra steps bring every stage to the same chunk,
             # which is what moving K/V state between stages requires
             phase(3 + rank, resident, keep_full=False)
-            planned = runner.plan_ranges("block" if args.block_split == "measured-blocks" else "half",
-                                         stage_ms=ref_stage)
+            planned = runner.plan_ranges("block" if args.block_split == "measured-blocks" else "half")
             runner.rebalance(planned, halves=True)
             phase(max(args.warmup, 1) + 2 + (world - 1 - rank), resident)     # re-record graphs, stagger again
             barrier()

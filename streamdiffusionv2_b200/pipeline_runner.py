@@ -21,7 +21,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from .ring_state import RingState
-from .stage_transport import StageLink, StagePacket, contiguous_block_ranges, partition_by_cost
+from .stage_transport import StageLink, StagePacket, contiguous_block_ranges, plan_from_measurements
 from .stream_pipeline import StreamPipeline, assign_ints
 
 
@@ -107,18 +107,12 @@ class PipelineStageRunner:
             self._measure_left -= 1
         return out
 
-    def plan_ranges(self, granularity: str = "half", stage_ms: Optional[float] = None) -> List[List[int]]:
-        """New stage ranges (half-block units) from measurements.  Every rank contributes, from its
-        launch-by-launch measured steps, the median time of each half block it ran and its stage's
-        extra time (everything that is not a block: embedding, row shift, head, x0 conversion,
-        re-noising); one all-gather on the default process group; then the same exact partition on
-        every rank (`partition_by_cost`).
-        With `stage_ms` - this rank's stage time per chunk in normal operation (graph replay
-        included), e.g. the median of `stage_events` - the launch-by-launch numbers are used only
-        as proportions (share of a block's two halves, extra work in units of a block) and the speed
-        of every stage is taken from `stage_ms`: GPUs of one node differ by several per cent under
-        their power caps, and launch-by-launch timing hides that.  Without it the launch-by-launch
-        times are used as they are.
+    def plan_ranges(self, granularity: str = "half") -> List[List[int]]:
+        """New stage ranges (half-block units) from the measured steps.  Every rank contributes the
+        median launch-by-launch time of each half block it ran and of its stage's extra work
+        (everything that is not a block: embedding, row shift, head, x0 conversion, re-noising); one
+        all-gather on the default process group; then the same exact partition on every rank
+        (`stage_transport.plan_from_measurements`, which uses the times as proportions only).
         granularity "block" keeps the boundaries at whole blocks.  Collective: call on every rank."""
         import statistics
         import torch.distributed as dist
@@ -141,39 +135,21 @@ class PipelineStageRunner:
                 per_half.setdefault(h, []).append(d)
                 inside += d
             extras.append(span(t0, t1) - inside)
-        mine = torch.zeros(n_half + 2, dtype=torch.float64)
+        mine = torch.zeros(n_half + 1, dtype=torch.float64)
         for h, v in per_half.items():
             mine[h] = statistics.median(v)
         mine[n_half] = max(statistics.median(extras), 0.0)
-        mine[n_half + 1] = -1.0 if stage_ms is None else float(stage_ms)
         mine = mine.to(dev)
         every = [torch.zeros_like(mine) for _ in range(self.world)]
         dist.all_gather(every, mine)
         every = [t.cpu() for t in every]
         costs = torch.stack([t[:n_half] for t in every]).max(dim=0).values.tolist()   # one rank measured each half
         overheads = [float(t[n_half]) for t in every]
-        stage_times = [float(t[n_half + 1]) for t in every]
         if min(costs) <= 0.0:
             raise RuntimeError("a half block was not measured on any rank")
-        step = 2 if granularity == "block" else 1
-        self.last_costs = {"per_half_ms": costs, "stage_extra_ms": overheads}
-        if min(stage_times) <= 0.0:
-            return partition_by_cost(costs, overheads, boundary_step=step)
-        # proportions from the launch-by-launch pass, speeds from normal operation: all blocks are the same
-        # layer, so one block = 1 unit, split between its halves as measured on average; a stage's extra work in
-        # units of its own mean block; its speed = its normal stage time per unit it currently holds
-        block_ms = [costs[2 * i] + costs[2 * i + 1] for i in range(n_half // 2)]
-        attn_share = statistics.mean(costs[2 * i] / block_ms[i] for i in range(n_half // 2))
-        units = [attn_share, 1.0 - attn_share] * (n_half // 2)
-        scales, extra_units = [], []
-        for r, (a, b) in enumerate(self.half_ranges):
-            mean_block = statistics.mean(block_ms[(a + 1) // 2:max((b + 1) // 2, (a + 1) // 2 + 1)])
-            x = overheads[r] / mean_block
-            scales.append(stage_times[r] / (sum(units[a:b]) + x))
-            extra_units.append(x)
-        self.last_costs.update(stage_ms=stage_times, ms_per_block=scales, stage_extra_blocks=extra_units,
-                               attention_share_of_block=attn_share)
-        return partition_by_cost(units, [s * x for s, x in zip(scales, extra_units)], boundary_step=step, scales=scales)
+        ranges, details = plan_from_measurements(costs, overheads, self.half_ranges, granularity)
+        self.last_costs = {"per_half_ms": costs, "stage_extra_ms": overheads, **details}
+        return ranges
 
     # ------------------------------------------------------------------ one chunk on this rank
     def step(self, chunk_idx: int = 0, noise: Optional[torch.Tensor] = None, current_start: Optional[int] = None,

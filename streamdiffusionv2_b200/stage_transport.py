@@ -128,6 +128,33 @@ def partition_by_cost(costs: Sequence[float], overheads: Sequence[float], bounda
     return out[::-1]
 
 
+def plan_from_measurements(per_half_ms: Sequence[float], stage_extra_ms: Sequence[float],
+                           half_ranges: Sequence[Sequence[int]], granularity: str = "half"):
+    """Stage ranges (half-block units) from one launch-by-launch measurement per half block and per
+    stage.  The measurements are used as proportions only: every block is the same layer, so a block
+    is one unit of work, split between its two halves in the ratio measured on average, and a stage's
+    extra work (embedding, head, re-noising ...) is expressed in units of the blocks measured on that
+    same stage, which cancels how fast or slow that stage happened to run while it was being measured.
+    All stages are then taken to be equally fast per unit: the GPUs of a node are the same part under
+    the same power cap, and a stage that looks faster in normal operation merely idles part of each
+    step and clocks higher while it works (measured on B200: a stage of 7 blocks ran at 1.66 ms per
+    block beside stages of 8 at 1.81, and the other way round after the blocks were moved).
+    Returns (ranges, details)."""
+    n_half = len(per_half_ms)
+    block_ms = [per_half_ms[2 * i] + per_half_ms[2 * i + 1] for i in range(n_half // 2)]
+    attn_share = sum(per_half_ms[2 * i] / block_ms[i] for i in range(n_half // 2)) / (n_half // 2)
+    units = [attn_share, 1.0 - attn_share] * (n_half // 2)
+    extra_units = []
+    for r, (a, b) in enumerate(half_ranges):
+        first, last = a // 2, max((b + 1) // 2, a // 2 + 1)          # blocks this stage ran at least half of
+        mean_block = sum(block_ms[first:last]) / (last - first)
+        extra_units.append(max(float(stage_extra_ms[r]), 0.0) / mean_block)
+    ranges = partition_by_cost(units, extra_units, boundary_step=2 if granularity == "block" else 1)
+    load = [extra_units[r] + sum(units[a:b]) for r, (a, b) in enumerate(ranges)]
+    return ranges, {"attention_share_of_block": attn_share, "stage_extra_blocks": extra_units,
+                    "planned_stage_load_blocks": load}
+
+
 class _Edge:
     """One direction of one ring edge as seen from this rank."""
 
