@@ -911,7 +911,7 @@ def main():
     ap.add_argument("--max-repeats", type=int, default=8)
     ap.add_argument("--no-graphs", dest="graphs", action="store_false",
                     help="launch every op of every step from Python instead of replaying steady steps from a CUDA graph")
-    ap.add_argument("--block-split", default="measured",
+    ap.add_argument("--block-split", default="reference",
                     choices=["reference", "balanced", "measured", "measured-blocks"],
                     help="N>1: reference = the reference's default block ranges (remainder on the first stages); "
                          "balanced = remainder on the middle stages; measured = start on the reference's split, time "
