@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -148,8 +149,11 @@ int attn_common(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, cons
   p.kv_row_broadcast = (k->stride_row == 0) ? 1 : 0;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = static_cast<int*>(workspace);
-  // scratch for split tail tiles, when the caller's workspace has room for it
-  if (workspace_bytes >= kStatusBytes + sdv2::kAttnMaxPartialSlots * sdv2::kAttnPartialBytesPerSlot) {
+  // measurement aid: with SDV2_ATTN_TRACE set, CTA 0 writes cycle stamps into the scratch area instead (no tail split)
+  static const bool trace = getenv("SDV2_ATTN_TRACE") != nullptr;
+  if (trace && workspace_bytes >= kStatusBytes + 256 * 32 * sizeof(long long)) {
+    p.trace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + kStatusBytes);
+  } else if (workspace_bytes >= kStatusBytes + sdv2::kAttnMaxPartialSlots * sdv2::kAttnPartialBytesPerSlot) {
     p.part_ml = reinterpret_cast<float*>(static_cast<char*>(workspace) + kStatusBytes);
     p.part_o = p.part_ml + static_cast<size_t>(sdv2::kAttnMaxPartialSlots) * 2 * 2 * 128;
   }

@@ -78,6 +78,9 @@ __device__ __forceinline__ void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint3
   }
 }
 
+// kTrace: CTA 0 records cycle stamps of its issuing thread and of one softmax thread per query tile
+// (a measurement aid, launched only when SDV2_ATTN_TRACE is set; the normal instantiation has none of it).
+template <bool kTrace>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
@@ -139,6 +142,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  auto stamp = [&](int j, int k) {
+    if (kTrace && blockIdx.x == 0 && p.trace != nullptr && j < 256) p.trace[j * 32 + k] = clock64();
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -206,13 +212,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const bool more = j + 1 < n_kv;
         bool v_next = false, k_next = false;
         for (int s = 0; s < n_stage && ok; ++s) {
+          stamp(j, s * 6 + 0);
           ok = mbar_wait(bar(kBarPHalf + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
+          stamp(j, s * 6 + 1);
           if (ok && s == 0 && !v_ready)
             ok = mbar_wait(bar(kBarKvFull + slot_v), par_v, abort_flag, p.status, WAIT_KV_FULL);
           if (!ok) break;
           tc_fence_after();
           issue_pv(tO[s], tS[s], slot_base(slot_v), j > 0, 0, 4);
+          stamp(j, s * 6 + 2);
           ok = mbar_wait(bar(kBarPFull + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
+          stamp(j, s * 6 + 3);
           if (ok && s == 0 && more && !k_ready)   // before the batch, so that its 12 MMAs go out back to back
             ok = mbar_wait(bar(kBarKvFull + slot_k), par_k, abort_flag, p.status, WAIT_KV_FULL);
           if (!ok) break;
@@ -220,10 +230,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           issue_pv(tO[s], tS[s], slot_base(slot_v), true, 4, 8);
           if (more) {
             issue_qk(tS[s], sq[s], slot_base(slot_k));
+            stamp(j, s * 6 + 4);
             umma_commit(bar(kBarSFull + s));
           } else {
             umma_commit(bar(kBarOFull + s));
           }
+          stamp(j, s * 6 + 5);
           if (s == n_stage - 1) {
             umma_commit(bar(kBarKvEmpty + slot_v));
             if (more) umma_commit(bar(kBarKvEmpty + slot_k));
@@ -257,9 +269,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       float l = 0.f;
       bool ok = true;
       for (int j = 0; j < n_kv; ++j) {
+        if (row == 0) stamp(j, 12 + stage * 6 + 0);
         ok = mbar_wait(bar(kBarSFull + stage), j & 1, abort_flag, p.status, WAIT_S_FULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (row == 0) stamp(j, 12 + stage * 6 + 1);
         tc_fence_after();
         uint32_t s[4][32];
 #pragma unroll
@@ -302,6 +316,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mx3 = fmaxf(mx3, __uint_as_float(s[c][i + 3]));
           }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;
+        if (row == 0) stamp(j, 12 + stage * 6 + 2);
         if (j == 0) {
           m_used = mx;  // tile 0 always has a valid column, so mx is finite
         } else {
@@ -340,11 +355,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(kBarPHalf + stage));
+            if (row == 0) stamp(j, 12 + stage * 6 + 3);
           }
         }
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(kBarPFull + stage));
+        if (row == 0) stamp(j, 12 + stage * 6 + 4);
         l += sum0 + sum1;
       }
       if (ok) {
@@ -572,11 +589,14 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const __grid_constant
 
 cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                                 const AttnParams& p_in, cudaStream_t stream) {
-  static DynamicSmemGrant smem_grant;
+  static DynamicSmemGrant smem_grant, smem_grant_trace;
   AttnParams p = p_in;
   DeviceInfo di;
   cudaError_t e = device_info(&di);
-  if (e == cudaSuccess) e = smem_grant.ensure(attn::attn_fwd_kernel, static_cast<int>(attn::kSmemBytes), di.device);
+  if (e == cudaSuccess)
+    e = p.trace != nullptr
+            ? smem_grant_trace.ensure(attn::attn_fwd_kernel<true>, static_cast<int>(attn::kSmemBytes), di.device)
+            : smem_grant.ensure(attn::attn_fwd_kernel<false>, static_cast<int>(attn::kSmemBytes), di.device);
   if (e != cudaSuccess) return e;
   p.pair_tiles = (p.q_tokens + 2 * attn::kBM - 1) / (2 * attn::kBM);
   const int64_t n_tiles = static_cast<int64_t>(p.pair_tiles) * p.heads * p.rows;
@@ -587,7 +607,10 @@ cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k
   p.split = attn_tail_split(n_tiles, di.sms, min_kv, p.part_o != nullptr, &p.n_tail);
   p.n_full = static_cast<int>(n_tiles) - p.n_tail;
   const unsigned grid = static_cast<unsigned>(p.n_full + p.n_tail * p.split);
-  attn::attn_fwd_kernel<<<grid, attn::kThreads, attn::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  if (p.trace != nullptr)
+    attn::attn_fwd_kernel<true><<<grid, attn::kThreads, attn::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  else
+    attn::attn_fwd_kernel<false><<<grid, attn::kThreads, attn::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
   e = cudaGetLastError();
   if (e != cudaSuccess || p.n_tail == 0) return e;
   attn_combine_kernel<<<dim3(p.n_tail, 2, attn::kBM / 32), 256, 0, stream>>>(p);

@@ -58,6 +58,7 @@ struct AttnParams {
   int n_full, n_tail, split;
   float* part_o;         // [n_tail * split][2][128][128] fp32
   float* part_ml;        // [n_tail * split][2][2][128] fp32: max (log2 units), sum
+  long long* trace;      // measurement builds only: cycle stamps of CTA 0, 32 per key tile; null otherwise
   int seq_lens[SDV2_MAX_ROWS];
 };
 

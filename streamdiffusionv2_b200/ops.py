@@ -404,7 +404,7 @@ def poll_status(device: torch.device) -> None:
     wrote nothing, so everything computed from its outputs is garbage).  Called by the attention
     forwards every few dozen launches and after every graph replay; not during stream capture."""
     device = torch.device(device)
-    if device.type != "cuda":
+    if device.type != "cuda" or torch.cuda.is_current_stream_capturing():
         return
     idx = device.index if device.index is not None else torch.cuda.current_device()
     p = _polls.get(idx)

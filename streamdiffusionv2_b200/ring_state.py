@@ -124,6 +124,10 @@ class RingState:
         when the number of cache rows changed); the device copy is authoritative afterwards."""
         rows = kv_cache["k"].shape[0]
         q = getattr(attn_module, "_sdv2_queue", None)
+        if q is not None and attn_module.evict_idx is not getattr(attn_module, "_sdv2_queue_host", None):
+            # somebody assigned a new `evict_idx` (the demo's cache resizer does, demo/vid2vid.py:146-148):
+            # the host lists are what counts now
+            attn_module._sdv2_queue = q = None
         if q is not None and (q.shape[0] != rows or q.device != torch.device(device)):
             RingState.pull_queue(attn_module)
             q = None
@@ -138,6 +142,7 @@ class RingState:
                     host[i, 1:1 + len(lst)] = torch.tensor([int(x) for x in lst], dtype=torch.int64)
             q = host.to(device)
             attn_module._sdv2_queue = q
+            attn_module._sdv2_queue_host = attn_module.evict_idx
         return q
 
     @staticmethod
@@ -149,6 +154,7 @@ class RingState:
             return
         host = q.cpu().tolist()
         attn_module.evict_idx = [[int(x) for x in row[1:1 + int(row[0])]] for row in host]
+        attn_module._sdv2_queue_host = attn_module.evict_idx
 
     @staticmethod
     def pull_queue(attn_module) -> None:

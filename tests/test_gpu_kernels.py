@@ -544,3 +544,26 @@ def test_frame_means_match_the_reference_reductions(dtype):
     m2 = ops.frame_means(big[:, :S], vc, kn, vn, sink, fs)
     assert torch.equal(m2, means)
     ops.read_status(torch.device("cuda"))
+
+
+def test_adaptive_queue_follows_a_replaced_evict_idx():
+    """With the adaptive sink test the evict queue is kept on the device, but `evict_idx` stays the
+    reference's attribute: a tool that assigns a new list (the demo's cache resizer copies row 0 to
+    every row, demo/vid2vid.py:146-148) must be obeyed from the next call on.  CUDA path and oracle
+    in lockstep, the same rewrite applied to both half-way."""
+    from streamdiffusionv2_b200 import causal_attention as ca
+    case = cases.KERNEL_CASES["k_bf16_adaptive"]
+    rewritten = False
+    for (i, _, _, cache, _, _, _), (j, out, kv, mod) in zip(replay_oracle(case), replay_cuda(case)):
+        assert i == j
+        st = cache.state
+        assert mod.evict_idx == st.evict_idx, i
+        assert kv["global_end_index"].tolist() == st.global_end and kv["local_end_index"].tolist() == st.local_end
+        assert cases.sha(kv["k"]) == cases.sha(cache.k), f"K cache differs at call {i}"
+        if i == 9:
+            rows = len(st.evict_idx)
+            st.evict_idx = [list(st.evict_idx[0]) + [4 * 6] for _ in range(rows)]      # row 0 everywhere, one more slot
+            mod.evict_idx = [list(r) for r in st.evict_idx]                             # a new list: what a tool would assign
+            rewritten = True
+    assert rewritten and i > 12
+    _ops().read_status(torch.device("cuda"))
