@@ -150,7 +150,8 @@ int attn_common(const sdv2_view* q, const sdv2_view* k, const sdv2_view* v, cons
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = static_cast<int*>(workspace);
   // measurement aid: with SDV2_ATTN_TRACE set, CTA 0 writes cycle stamps into the scratch area instead (no tail split)
-  static const bool trace = getenv("SDV2_ATTN_TRACE") != nullptr;
+  static const int trace = getenv("SDV2_ATTN_TRACE") ? atoi(getenv("SDV2_ATTN_TRACE")) : 0;
+  p.trace_mode = trace;
   if (trace && workspace_bytes >= kStatusBytes + 256 * 32 * sizeof(long long)) {
     p.trace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + kStatusBytes);
   } else if (workspace_bytes >= kStatusBytes + sdv2::kAttnMaxPartialSlots * sdv2::kAttnPartialBytesPerSlot) {

@@ -1,7 +1,8 @@
 // Attention of new queries over the K/V cache on the sm_100a tensor cores.
 //
 // One CTA per (pair of 128-row query tiles, head, cache row).  Warp roles:
-//   warp 0      TMA producer: Q tiles once, then K_j / V_j tiles through a ring of 32 KB slots
+//   warp 0      TMA producer: Q tiles once, then K_0 and the pairs (V_j, K_{j+1}) through a ring of 32 KB slots;
+//               a pair is what one key-tile step consumes, so it has one "landed" and one "released" barrier
 //   warp 1      MMA issuer (one thread): S = Q K^T and O += P V with tcgen05.mma, fp32 in TMEM
 //   warps 4-7   softmax for query tile 0 (one thread per query row = one TMEM lane)
 //   warps 8-11  softmax for query tile 1
@@ -41,16 +42,21 @@ constexpr uint32_t kSmemBytes = kSmemBar + 256 + 1024;  // + alignment slack
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256;
 
-// barrier indices
-constexpr int kBarQFull = 0;                   // [2]
-constexpr int kBarKvFull = 2;                  // [kSlots]
-constexpr int kBarKvEmpty = 2 + kSlots;        // [kSlots]
-constexpr int kBarSFull = 2 + 2 * kSlots;      // [2]
-constexpr int kBarPFull = kBarSFull + 2;       // [2]
-constexpr int kBarOFull = kBarPFull + 2;       // [2]
-constexpr int kBarPHalf = kBarOFull + 2;       // [2] first 64 key columns of P written
+// barrier indices.  K_0 has a barrier of its own; after it the ring carries pairs (V_g, K_{g+1}), the two
+// tiles one key-tile step of the issuer consumes and releases together, so that step needs one wait and
+// one commit for both.  Three barriers of each kind suffice: the producer is at most two pairs ahead.
+constexpr int kPairBars = 3;
+constexpr int kBarQFull = 0;                        // [2]
+constexpr int kBarK0Full = 2;                       // K_0 landed
+constexpr int kBarPairFull = 3;                     // [kPairBars] V_g and K_{g+1} landed
+constexpr int kBarPairDone = 3 + kPairBars;         // [kPairBars] every MMA reading V_g or K_{g+1} (or older) completed
+constexpr int kBarSFull = 3 + 2 * kPairBars;        // [2]
+constexpr int kBarPFull = kBarSFull + 2;            // [2]
+constexpr int kBarOFull = kBarPFull + 2;            // [2]
+constexpr int kBarPHalf = kBarOFull + 2;            // [2] first 64 key columns of P written
 constexpr int kNumBars = kBarPHalf + 2;
 static_assert(kNumBars * 8 + 16 <= 256, "barrier block too small");
+static_assert(kSlots >= 5, "pair g overwrites the tiles of pairs g-3 and g-2: needs five slots");
 
 constexpr uint32_t kIdescQK = umma_idesc_bf16(kBM, kBN, false, false);
 constexpr uint32_t kIdescPV = umma_idesc_bf16(kBM, kHD, false, true);
@@ -69,12 +75,17 @@ __device__ __forceinline__ void issue_qk(uint32_t tmem_s, uint32_t sq, uint32_t 
 // O[stage] (+)= P[stage] (128 x 128 bf16 in TMEM, 8 columns per K step) * V_tile (kv x d, MN-major).
 // k_begin..k_end select 16-key steps, so that the first half of a tile can be issued while the
 // softmax warps are still producing the second half of P.
+// a_from_smem (the rate measurement only): A is the K-major shared-memory tile at sa instead of P.
 __device__ __forceinline__ void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t sv, bool accumulate,
-                                         int k_begin = 0, int k_end = 8) {
+                                         int k_begin = 0, int k_end = 8, bool a_from_smem = false, uint32_t sa = 0) {
 #pragma unroll
   for (int k = k_begin; k < k_end; ++k) {
-    umma_ts(tmem_o, tmem_p + k * 8, umma_smem_desc(sv + k * 2048, kHalfTile, 1024), kIdescPV,
-            (accumulate || k > k_begin) ? 1u : 0u);
+    const uint32_t acc = (accumulate || k > k_begin) ? 1u : 0u;
+    const uint64_t b_desc = umma_smem_desc(sv + k * 2048, kHalfTile, 1024);
+    if (a_from_smem)
+      umma_ss(tmem_o, umma_smem_desc(sa + (k >> 2) * kHalfTile + (k & 3) * 32, 16, 1024), b_desc, kIdescPV, acc);
+    else
+      umma_ts(tmem_o, tmem_p + k * 8, b_desc, kIdescPV, acc);
   }
 }
 
@@ -119,9 +130,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 2; ++i) mbar_init(bar(kBarQFull + i), 1);
-    for (int i = 0; i < kSlots; ++i) {
-      mbar_init(bar(kBarKvFull + i), 1);
-      mbar_init(bar(kBarKvEmpty + i), 1);
+    mbar_init(bar(kBarK0Full), 1);
+    for (int i = 0; i < kPairBars; ++i) {
+      mbar_init(bar(kBarPairFull + i), 1);
+      mbar_init(bar(kBarPairDone + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(kBarSFull + i), 1);
@@ -156,26 +168,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_4d(base + kSmemQ + s * kTileBytes + kHalfTile, &tm_q, bar(kBarQFull + s), 64, h,
                     q0 + s * kBM, b);
       }
+      auto slot_addr = [&](int it) { return base + kSmemKV + (it % kSlots) * kTileBytes; };
+      auto load_tile = [&](const CUtensorMap* tm, int it, int kv_tile, uint32_t full_bar) {
+        tma_load_4d(slot_addr(it), tm, full_bar, 0, h, (j0 + kv_tile) * kBN, bk);
+        tma_load_4d(slot_addr(it) + kHalfTile, tm, full_bar, 64, h, (j0 + kv_tile) * kBN, bk);
+      };
+      mbar_expect_tx(bar(kBarK0Full), kTileBytes);
+      load_tile(&tm_k, 0, 0, bar(kBarK0Full));
       bool ok = true;
-      int issued = 0;
-      for (int it = 0; it < 2 * n_kv && ok; ++it) {  // even: K_{it/2}, odd: V_{it/2}
-        const int slot = it % kSlots;
-        const int use = it / kSlots;
-        if (use > 0) ok = mbar_wait(bar(kBarKvEmpty + slot), (use - 1) & 1, abort_flag, p.status, WAIT_KV_EMPTY);
+      int issued = 0;  // pairs requested
+      for (int g = 0; g < n_kv && ok; ++g) {  // pair g = items 2g+1 (V_g) and 2g+2 (K_{g+1})
+        // the slots of pair g held K_{g-2} and V_{g-2}: free once step g-2 of the issuer has completed
+        if (g >= 2)
+          ok = mbar_wait(bar(kBarPairDone + (g - 2) % kPairBars), ((g - 2) / kPairBars) & 1, abort_flag, p.status,
+                         WAIT_KV_EMPTY);
         if (!ok) break;
-        const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
-        const uint32_t dst = base + kSmemKV + slot * kTileBytes;
-        mbar_expect_tx(bar(kBarKvFull + slot), kTileBytes);
-        tma_load_4d(dst, tm, bar(kBarKvFull + slot), 0, h, (j0 + (it >> 1)) * kBN, bk);
-        tma_load_4d(dst + kHalfTile, tm, bar(kBarKvFull + slot), 64, h, (j0 + (it >> 1)) * kBN, bk);
-        issued = it + 1;
+        const bool more = g + 1 < n_kv;
+        const uint32_t full = bar(kBarPairFull + g % kPairBars);
+        mbar_expect_tx(full, more ? 2 * kTileBytes : kTileBytes);
+        load_tile(&tm_v, 2 * g + 1, g, full);
+        if (more) load_tile(&tm_k, 2 * g + 2, g + 1, full);
+        issued = g + 1;
       }
       if (!ok) {
         // leave no copy in flight: wait (bounded) for the tiles already requested
-        for (int it = (issued > kSlots ? issued - kSlots : 0); it < issued; ++it) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(bar(kBarKvFull + it % kSlots), (it / kSlots) & 1) &&
-                 clock64() - t0 < kWaitBudgetCycles) {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar(kBarK0Full), 0) && clock64() - t0 < kWaitBudgetCycles) {
+        }
+        for (int g = (issued > kPairBars ? issued - kPairBars : 0); g < issued; ++g) {
+          const long long t1 = clock64();
+          while (!mbar_try_wait(bar(kBarPairFull + g % kPairBars), (g / kPairBars) & 1) &&
+                 clock64() - t1 < kWaitBudgetCycles) {
           }
         }
       }
@@ -188,7 +211,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t tS[2] = {tmem + kColS, tmem + kColS + 128};
       const uint32_t tO[2] = {tmem + kColO, tmem + kColO + 128};
       auto slot_addr = [&](int it) { return base + kSmemKV + (it % kSlots) * kTileBytes; };
-      bool ok = mbar_wait(bar(kBarKvFull + 0), 0, abort_flag, p.status, WAIT_KV_FULL);
+      bool ok = mbar_wait(bar(kBarK0Full), 0, abort_flag, p.status, WAIT_KV_FULL);
       for (int s = 0; s < n_stage && ok; ++s) {
         ok = mbar_wait(bar(kBarQFull + s), 0, abort_flag, p.status, WAIT_Q_FULL);
         if (!ok) break;
@@ -196,63 +219,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         issue_qk(tS[s], sq[s], slot_addr(0));
         umma_commit(bar(kBarSFull + s));
       }
-      if (ok) umma_commit(bar(kBarKvEmpty + 0));
-      // ring position (slot, phase parity) of V_j and K_{j+1}, advanced by two items per key tile
-      int slot_v = 1 % kSlots, par_v = 0, slot_k = 2 % kSlots, par_k = 0;
-      auto advance = [](int& slot, int& par) {
-        slot += 2;
-        if (slot >= kSlots) {
-          slot -= kSlots;
-          par ^= 1;
-        }
-      };
-      auto slot_base = [&](int slot) { return base + kSmemKV + slot * kTileBytes; };
-      bool v_ready = false, k_ready = false;  // already seen complete by an early probe
+      // step j: O += P_j V_j and S = Q K_{j+1}^T for each query tile; V_j and K_{j+1} are pair j of the ring
+      int slot_v = 1 % kSlots, slot_k = 2 % kSlots, pair_bar = 0, pair_par = 0;
       for (int j = 0; j < n_kv && ok; ++j) {
         const bool more = j + 1 < n_kv;
-        bool v_next = false, k_next = false;
+        const uint32_t sv = base + kSmemKV + slot_v * kTileBytes, sk = base + kSmemKV + slot_k * kTileBytes;
         for (int s = 0; s < n_stage && ok; ++s) {
           stamp(j, s * 6 + 0);
           ok = mbar_wait(bar(kBarPHalf + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
           stamp(j, s * 6 + 1);
-          if (ok && s == 0 && !v_ready)
-            ok = mbar_wait(bar(kBarKvFull + slot_v), par_v, abort_flag, p.status, WAIT_KV_FULL);
+          if (ok && s == 0) ok = mbar_wait(bar(kBarPairFull + pair_bar), pair_par, abort_flag, p.status, WAIT_KV_FULL);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(tO[s], tS[s], slot_base(slot_v), j > 0, 0, 4);
+          issue_pv(tO[s], tS[s], sv, j > 0, 0, 4);
           stamp(j, s * 6 + 2);
           ok = mbar_wait(bar(kBarPFull + s), j & 1, abort_flag, p.status, WAIT_P_FULL);
           stamp(j, s * 6 + 3);
-          if (ok && s == 0 && more && !k_ready)   // before the batch, so that its 12 MMAs go out back to back
-            ok = mbar_wait(bar(kBarKvFull + slot_k), par_k, abort_flag, p.status, WAIT_KV_FULL);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(tO[s], tS[s], slot_base(slot_v), true, 4, 8);
+          issue_pv(tO[s], tS[s], sv, true, 4, 8);
           if (more) {
-            issue_qk(tS[s], sq[s], slot_base(slot_k));
+            issue_qk(tS[s], sq[s], sk);
             stamp(j, s * 6 + 4);
             umma_commit(bar(kBarSFull + s));
           } else {
             umma_commit(bar(kBarOFull + s));
           }
           stamp(j, s * 6 + 5);
-          if (s == n_stage - 1) {
-            umma_commit(bar(kBarKvEmpty + slot_v));
-            if (more) umma_commit(bar(kBarKvEmpty + slot_k));
-          }
-          if (s == 0 && more) {
-            // this tile's MMAs are queued: probe the next tile's operands while they run
-            int sv = slot_v, pv = par_v, sk = slot_k, pk = par_k;
-            advance(sv, pv);
-            advance(sk, pk);
-            v_next = mbar_test_wait(bar(kBarKvFull + sv), pv);
-            k_next = j + 2 < n_kv && mbar_test_wait(bar(kBarKvFull + sk), pk);
-          }
         }
-        advance(slot_v, par_v);
-        advance(slot_k, par_k);
-        v_ready = v_next;
-        k_ready = k_next;
+        if (ok) umma_commit(bar(kBarPairDone + pair_bar));
+        slot_v = slot_v + 2 >= kSlots ? slot_v + 2 - kSlots : slot_v + 2;
+        slot_k = slot_k + 2 >= kSlots ? slot_k + 2 - kSlots : slot_k + 2;
+        if (++pair_bar == kPairBars) {
+          pair_bar = 0;
+          pair_par ^= 1;
+        }
       }
     }
   } else if (warp >= 4) {
@@ -291,7 +292,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // Query tile 0 clears them in shared memory before it reports P (tile 1's P V is issued later).
           if (stage == 0) {
             const int it_v = 2 * j + 1;
-            ok = mbar_wait(bar(kBarKvFull + it_v % kSlots), (it_v / kSlots) & 1, abort_flag, p.status, WAIT_KV_FULL);
+            ok = mbar_wait(bar(kBarPairFull + j % kPairBars), (j / kPairBars) & 1, abort_flag, p.status, WAIT_KV_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (row >= valid) {
@@ -538,6 +539,94 @@ __global__ void __launch_bounds__(32, 1) wait_timeout_selftest_kernel(int* statu
   if (threadIdx.x != 0) mbar_wait(bar, 0, abort_flag, nullptr, WAIT_PROBE, budget);
 }
 
+// Measurement aid (SDV2_ATTN_TRACE with bit 8): every CTA issues runs of 64 MMAs of one kind back to back
+// on real tiles and records the cycles from the first issue to the completion of the last one.
+//   0 SS K-major N=128   1 TS + MN-major B N=128   2 SS, MN-major B   3 kinds 0 and 1 alternating by fours
+//   4 SS K-major N=64    5 SS K-major N=256 (B rows past 128 are whatever follows the tile)
+__global__ void __launch_bounds__(128, 1)
+umma_rate_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw);
+  const uint32_t sQ = base, sK = base + kTileBytes, sK2 = base + 2 * kTileBytes, sV = base + 3 * kTileBytes;
+  const uint32_t bar0 = base + 4 * kTileBytes;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 4 * kTileBytes + 64);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + 4 * kTileBytes + 68);
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar0, 1);
+    mbar_init(bar0 + 8, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  if (threadIdx.x == 0) {
+    const int h = blockIdx.x % p.heads;
+    mbar_expect_tx(bar0, 4 * kTileBytes);
+    for (int half = 0; half < 2; ++half) {
+      tma_load_4d(sQ + half * kHalfTile, &tm_q, bar0, 64 * half, h, 0, 0);
+      tma_load_4d(sK + half * kHalfTile, &tm_k, bar0, 64 * half, h, 0, 0);
+      tma_load_4d(sK2 + half * kHalfTile, &tm_k, bar0, 64 * half, h, 128, 0);
+      tma_load_4d(sV + half * kHalfTile, &tm_v, bar0, 64 * half, h, 0, 0);
+    }
+    bool ok = mbar_wait(bar0, 0, abort_flag, p.status, WAIT_PROBE);
+    constexpr uint32_t kIdesc64 = umma_idesc_bf16(kBM, 64, false, false);
+    constexpr uint32_t kIdesc256 = umma_idesc_bf16(kBM, 256, false, false);
+    uint32_t parity = 0;
+    for (int v = 0; v < 8 && ok; ++v) {
+      tc_fence_after();
+      const long long t0 = clock64();
+      for (int rep = 0; rep < 8; ++rep) {
+        if (v == 0) issue_qk(tmem + kColS, sQ, sK);
+        if (v == 1) issue_pv(tmem + kColO, tmem + kColS + 128, sV, rep > 0);
+        if (v == 2) issue_pv(tmem + kColO, 0, sV, rep > 0, 0, 8, true, sQ);
+        if (v == 3) {
+          issue_pv(tmem + kColO, tmem + kColS + 128, sV, rep > 0, 0, 4);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t off = (k & 3) * 32;
+            umma_ss(tmem + kColS, umma_smem_desc(sQ + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024), kIdescQK,
+                    k > 0 ? 1u : 0u);
+          }
+        }
+        if (v == 6 && rep < 4) {  // 6: whole P V then whole Q K^T, as the kernel orders them
+          issue_pv(tmem + kColO, tmem + kColS + 128, sV, rep > 0);
+          issue_qk(tmem + kColS, sQ, sK);
+        }
+        if (v == 7) issue_qk(tmem + kColS + (rep & 1) * 128, sQ, sK);  // 7: kind 0, two accumulators in turn
+        if (v == 4 || v == 5) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * kHalfTile + (k & 3) * 32;
+            umma_ss(tmem + kColS, umma_smem_desc(sQ + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024),
+                    v == 4 ? kIdesc64 : kIdesc256, k > 0 ? 1u : 0u);
+          }
+        }
+      }
+      umma_commit(bar0 + 8);
+      ok = mbar_wait(bar0 + 8, parity, abort_flag, p.status, WAIT_PROBE);
+      parity ^= 1;
+      const long long t1 = clock64();
+      if (blockIdx.x < 16) p.trace[blockIdx.x * 8 + v] = t1 - t0;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
 }  // namespace attn
 
 // Merge the partial results of the split tail tiles.  Block = (tail tile, query tile, group of 32
@@ -598,6 +687,14 @@ cudaError_t launch_attn_tcgen05(const CUtensorMap& tm_q, const CUtensorMap& tm_k
             ? smem_grant_trace.ensure(attn::attn_fwd_kernel<true>, static_cast<int>(attn::kSmemBytes), di.device)
             : smem_grant.ensure(attn::attn_fwd_kernel<false>, static_cast<int>(attn::kSmemBytes), di.device);
   if (e != cudaSuccess) return e;
+  if (p.trace != nullptr && (p.trace_mode & 256)) {
+    static DynamicSmemGrant rate_grant;
+    const int smem = 4 * attn::kTileBytes + 128 + 1024;
+    e = rate_grant.ensure(attn::umma_rate_kernel, smem, di.device);
+    if (e != cudaSuccess) return e;
+    attn::umma_rate_kernel<<<di.sms, 128, smem, stream>>>(tm_q, tm_k, tm_v, p);
+    return cudaGetLastError();
+  }
   p.pair_tiles = (p.q_tokens + 2 * attn::kBM - 1) / (2 * attn::kBM);
   const int64_t n_tiles = static_cast<int64_t>(p.pair_tiles) * p.heads * p.rows;
   if (n_tiles > 0x7FFFFFFFLL) return cudaErrorInvalidValue;

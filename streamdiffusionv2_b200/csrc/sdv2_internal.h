@@ -59,6 +59,7 @@ struct AttnParams {
   float* part_o;         // [n_tail * split][2][128][128] fp32
   float* part_ml;        // [n_tail * split][2][2][128] fp32: max (log2 units), sum
   long long* trace;      // measurement builds only: cycle stamps of CTA 0, 32 per key tile; null otherwise
+  int trace_mode;        // with trace: bit 8 (256) runs the MMA rate measurement instead of the attention
   int seq_lens[SDV2_MAX_ROWS];
 };
 
