@@ -758,7 +758,7 @@ def run_pipeline(args):
             # with every half block timed, one all-gather, the exact partition, blocks moved with their K/V
             runner.stage_events = []
             ref_ms = max_over_ranks([region(resident)])[0]
-            ref_stage = statistics.mean(a.elapsed_time(b) for a, b in runner.stage_events)
+            ref_stage = statistics.median(a.elapsed_time(b) for a, b in runner.stage_events)
             per_stage = [torch.zeros(1, dtype=torch.float64, device=device) for _ in range(world)]
             dist.all_gather(per_stage, torch.tensor([ref_stage], dtype=torch.float64, device=device))
             reference_split = {"stage_blocks": [list(r) for r in runner.block_ranges],
@@ -789,7 +789,7 @@ def run_pipeline(args):
         regions = [first_ms] + max_over_ranks([region(resident) for _ in range(repeats - 1)])
         clocks = sampler.stop() if rank == 0 else None
         ms = statistics.median(regions)
-        stage_ms = statistics.mean(a.elapsed_time(b) for a, b in runner.stage_events)
+        stage_ms = statistics.median(a.elapsed_time(b) for a, b in runner.stage_events)  # a step that records its graph is an outlier
         runner.stage_events = None
 
         # host buffers in, host result out, every step; chunk latency from wall-clock-anchored device events:
