@@ -277,6 +277,10 @@ int sdv2_attn_kvcache_static(const sdv2_view* q, const sdv2_view* k_cache, const
  *   mod_row_stride elements after the previous one (6 * dim in place, dim if copied out).
  * sdv2_gate_residual: out = bf16(x + bf16(y * gate[b,f])) - the gated residual after them
  *   (models/wan/causal_model.py:470-471, 482-483); gate addressed like scale.  out may alias x.
+ * sdv2_layernorm_affine: out[r,:] = bf16(weight * ((x[r,:] - mean) * rstd) + bias) in fp32 - torch.nn.LayerNorm
+ *   with elementwise_affine on bf16 tensors, the block's norm3 in front of the text cross-attention
+ *   (models/wan/causal_model.py:473-476; WanLayerNorm, models/wan/wan_base/modules/model.py:89-100);
+ *   x, out contiguous [n_rows, dim], dim at most 5120.
  * dim must be a multiple of 8 and at most 8192; all pointers 16-byte aligned.
  */
 int sdv2_rmsnorm(const void* x, int64_t x_row_stride, const void* weight, void* out, int64_t out_row_stride,
@@ -285,6 +289,8 @@ int sdv2_ln_modulate(const void* x, const void* scale, const void* shift, int64_
                      int batch, int frames, int tokens_per_frame, int dim, float eps, void* stream);
 int sdv2_gate_residual(const void* x, const void* y, const void* gate, int64_t mod_row_stride, void* out, int batch,
                        int frames, int tokens_per_frame, int dim, void* stream);
+int sdv2_layernorm_affine(const void* x, const void* weight, const void* bias, void* out, int64_t n_rows, int dim,
+                          float eps, void* stream);
 
 /* Synchronises `stream`, reads the status word at the start of a workspace and clears it.
  * Returns SDV2_OK, SDV2_ERR_TIMEOUT (a device-side wait ran out; *detail = where),

@@ -305,7 +305,9 @@ def block_forward(self, x, e, seq_lens, grid_sizes, freqs, context, context_lens
     y = self.self_attn(norm_modulate(self.norm1, x, scale_a, shift_a), seq_lens, grid_sizes, freqs, block_mask,
                        kv_cache, current_start, current_end, causal_rope_cache)
     x = add_gated(x, y, gate_a)
-    x = x + self.cross_attn(self.norm3(x), context, context_lens, crossattn_cache=crossattn_cache)
+    xn = ops.layernorm_affine(x, self.norm3.weight, self.norm3.bias, self.norm3.eps) \
+        if fused and ops.can_fuse_layernorm(x, self.norm3) else self.norm3(x)
+    x = x + self.cross_attn(xn, context, context_lens, crossattn_cache=crossattn_cache)
     y = self.ffn(norm_modulate(self.norm2, x, scale_f, shift_f))
     return add_gated(x, y, gate_f)
 

@@ -6,8 +6,9 @@
 //   rmsnorm        : bf16( bf16(x * rsqrt(mean(x^2) + eps)) * w )                     per token row
 //   ln_modulate    : bf16( bf16( bf16(LN(x)) * bf16(1 + scale[b, frame]) ) + shift[b, frame] )  per token row
 //   gate_residual  : bf16( x + bf16(y * gate[b, frame]) )                              per element
+//   layernorm_affine: bf16( w * ((x - mean) * rstd) + b )                             per token row
 //
-// All three are pure streaming kernels (one read and one write of [tokens, dim], plus y for the
+// All of them are pure streaming kernels (one read and one write of [tokens, dim], plus y for the
 // last), bound by HBM bandwidth; 16-byte vector accesses, one token row per block for the two
 // normalisations.
 #include <cuda_bf16.h>
@@ -144,6 +145,107 @@ __global__ void __launch_bounds__(kRowThreads) row_norm_kernel(const __grid_cons
   }
 }
 
+// LayerNorm with one warp per token row: the row stays in registers between the two statistics passes and
+// the output pass, the reductions are shuffles only (no block barrier), and each lane has kVecPerLane
+// independent 16-byte loads in flight.  kAffine = false: the adaLN modulation of ln_modulate;
+// kAffine = true: out = bf16(weight * ((x - mean) * rstd) + bias) with fp32 arithmetic, the formula of
+// torch.nn.LayerNorm on bf16 tensors (norm3 of the block, models/wan/causal_model.py:473-476).
+constexpr int kLnWarps = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int kVecPerLane, bool kAffine>
+__global__ void __launch_bounds__(kLnWarps * 32) ln_rows_kernel(const __grid_constant__ RowParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + (threadIdx.x >> 5);
+  if (row >= p.n_rows) return;
+  const int n_vec = p.dim >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(p.x + row * p.x_stride);
+  uint4 v[kVecPerLane];
+#pragma unroll
+  for (int i = 0; i < kVecPerLane; ++i) {
+    const int c = lane + i * 32;
+    v[i] = c < n_vec ? xr[c] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < kVecPerLane; ++i) {
+    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s += lo_f(w[j]) + hi_f(w[j]);
+  }
+  const float mean = warp_sum(s) / p.dim;
+  float d2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < kVecPerLane; ++i) {
+    if (lane + i * 32 < n_vec) {
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = lo_f(w[j]) - mean, b = hi_f(w[j]) - mean;
+        d2 += a * a + b * b;
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(d2) / p.dim + p.eps);
+  const uint4* mul;
+  const uint4* add;
+  if (kAffine) {
+    mul = reinterpret_cast<const uint4*>(p.w);
+    add = reinterpret_cast<const uint4*>(p.shift);
+  } else {
+    const int64_t b = row / p.tokens_per_batch;
+    const int f = static_cast<int>((row - b * p.tokens_per_batch) / p.tokens_per_frame);
+    const int64_t off = (b * p.frames + f) * p.mod_stride;
+    mul = reinterpret_cast<const uint4*>(p.scale1p + off);
+    add = reinterpret_cast<const uint4*>(p.shift + off);
+  }
+  uint4* orow = reinterpret_cast<uint4*>(p.out + row * p.out_stride);
+#pragma unroll
+  for (int i = 0; i < kVecPerLane; ++i) {
+    const int c = lane + i * 32;
+    if (c < n_vec) {
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+      const uint4 m4 = __ldg(mul + c), a4 = __ldg(add + c);
+      const uint32_t m[4] = {m4.x, m4.y, m4.z, m4.w}, a[4] = {a4.x, a4.y, a4.z, a4.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        if (kAffine) {
+          lo = lo_f(m[j]) * (rstd * (lo_f(w[j]) - mean)) + lo_f(a[j]);
+          hi = hi_f(m[j]) * (rstd * (hi_f(w[j]) - mean)) + hi_f(a[j]);
+        } else {
+          lo = bf16_round(bf16_round((lo_f(w[j]) - mean) * rstd) * bf16_round(1.f + lo_f(m[j]))) + lo_f(a[j]);
+          hi = bf16_round(bf16_round((hi_f(w[j]) - mean) * rstd) * bf16_round(1.f + hi_f(m[j]))) + hi_f(a[j]);
+        }
+        o[j] = pack_bf16x2(lo, hi);
+      }
+      orow[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// Picks the instantiation whose lanes hold the whole row; false when the row is longer than any of them.
+template <bool kAffine>
+bool launch_ln_rows(const RowParams& p, cudaStream_t stream) {
+  const int per_lane = ((p.dim >> 3) + 31) / 32;
+  const unsigned grid = static_cast<unsigned>((p.n_rows + kLnWarps - 1) / kLnWarps);
+  if (per_lane <= 6)
+    ln_rows_kernel<6, kAffine><<<grid, kLnWarps * 32, 0, stream>>>(p);
+  else if (per_lane <= 8)
+    ln_rows_kernel<8, kAffine><<<grid, kLnWarps * 32, 0, stream>>>(p);
+  else if (per_lane <= 20)
+    ln_rows_kernel<20, kAffine><<<grid, kLnWarps * 32, 0, stream>>>(p);
+  else
+    return false;
+  return true;
+}
+
 struct GateParams {
   const __nv_bfloat16* x;
   const __nv_bfloat16* y;
@@ -227,8 +329,27 @@ extern "C" int sdv2_ln_modulate(const void* x, const void* scale1p, const void* 
   p.frames = frames;
   p.tokens_per_frame = tokens_per_frame;
   p.tokens_per_batch = frames * tokens_per_frame;
-  sdv2::row_norm_kernel<true><<<static_cast<unsigned>(n_rows), sdv2::kRowThreads, 0,
-                                static_cast<cudaStream_t>(stream)>>>(p);
+  if (!sdv2::launch_ln_rows<false>(p, static_cast<cudaStream_t>(stream)))  // rows of more than 5120 elements
+    sdv2::row_norm_kernel<true><<<static_cast<unsigned>(n_rows), sdv2::kRowThreads, 0,
+                                  static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
+}
+
+extern "C" int sdv2_layernorm_affine(const void* x, const void* weight, const void* bias, void* out, int64_t n_rows,
+                                     int dim, float eps, void* stream) {
+  if (!x || !weight || !bias || !out || n_rows <= 0 || dim <= 0) return SDV2_ERR_INVALID_ARG;
+  if (dim % 8 || dim > 5120 || n_rows > 0x7FFFFFFFLL) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  if (!a16(x) || !a16(weight) || !a16(bias) || !a16(out)) return SDV2_ERR_MISALIGNED;
+  sdv2::RowParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.x_stride = p.out_stride = dim;
+  p.n_rows = n_rows;
+  p.dim = dim;
+  p.eps = eps;
+  p.w = static_cast<const __nv_bfloat16*>(weight);
+  p.shift = static_cast<const __nv_bfloat16*>(bias);
+  if (!sdv2::launch_ln_rows<true>(p, static_cast<cudaStream_t>(stream))) return SDV2_ERR_UNSUPPORTED_SHAPE;
   return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
 }
 

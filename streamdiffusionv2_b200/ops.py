@@ -342,6 +342,28 @@ def ln_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, frame
     return out
 
 
+def layernorm_affine(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
+    """torch.nn.LayerNorm with weight and bias over the last dimension of a bf16 tensor, one launch."""
+    dim = x.shape[-1]
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    with _Logged("layernorm_affine", 2.0 * x.numel() * 2):
+        rc = N.lib().sdv2_layernorm_affine(x.data_ptr(), weight.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                                           x.numel() // dim, dim, eps, N.stream_ptr(x.device))
+    N.check(rc, "sdv2_layernorm_affine")
+    return out
+
+
+def can_fuse_layernorm(x: torch.Tensor, norm) -> bool:
+    """Whether `norm` (an affine LayerNorm over the last dimension) applied to `x` can run as
+    `layernorm_affine`."""
+    w, b = getattr(norm, "weight", None), getattr(norm, "bias", None)
+    return (w is not None and b is not None and x.is_cuda and x.dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and w.is_contiguous() and b.is_contiguous()
+            and x.shape[-1] % 8 == 0 and x.shape[-1] <= 5120 and tuple(getattr(norm, "normalized_shape", ())) ==
+            (x.shape[-1],))
+
+
 def gate_residual(x: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, frames: int) -> torch.Tensor:
     """bf16(x + bf16(y * gate)) with per-frame gate [B, frames, (1,) dim] read in place."""
     B, L, dim = x.shape

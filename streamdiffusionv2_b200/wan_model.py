@@ -118,14 +118,18 @@ class DiTBlock(nn.Module):
         self.ffn = nn.Sequential(nn.Linear(dim, ffn_dim), nn.GELU(approximate="tanh"), nn.Linear(ffn_dim, dim))
         self.modulation = nn.Parameter(torch.randn(1, 6, dim) / dim ** 0.5)
 
-    def forward(self, x, e, grid_sizes, freqs, context, kv_cache, crossattn_cache, current_start, part="all"):
-        """x [B, L, C]; e [B, F, 6, C] (per-frame modulation from the timestep embedding).
+    def forward(self, x, e, grid_sizes, freqs, context, kv_cache, crossattn_cache, current_start, part="all",
+                modulated=None):
+        """x [B, L, C]; e [B, F, 6, C] (per-frame modulation from the timestep embedding); `modulated`, when
+        given, is `self.modulation.unsqueeze(1) + e` computed by the caller (for all its blocks in one launch).
         `part` runs the block in two halves for pipeline stages that meet inside a block: "attn" ends
         after the self-attention residual (causal_model.py:463-471), "rest" resumes there (cross-
         attention and FFN, :473-483); "attn" then "rest" computes exactly what "all" does."""
         frames = e.shape[1]
         per_frame = x.shape[1] // frames
-        shift_a, scale_a, gate_a, shift_f, scale_f, gate_f = (self.modulation.unsqueeze(1) + e).chunk(6, dim=2)
+        if modulated is None:
+            modulated = self.modulation.unsqueeze(1) + e
+        shift_a, scale_a, gate_a, shift_f, scale_f, gate_f = modulated.chunk(6, dim=2)
 
         fused = _fusable(x) and shift_a.dtype == torch.bfloat16
 
@@ -145,7 +149,9 @@ class DiTBlock(nn.Module):
             x = add_gated(x, y, gate_a)
             if part == "attn":
                 return x
-        x = x + self.cross_attn(self.norm3(x), context, None, crossattn_cache=crossattn_cache)
+        xn = ops.layernorm_affine(x, self.norm3.weight, self.norm3.bias, self.norm3.eps) \
+            if fused and ops.can_fuse_layernorm(x, self.norm3) else self.norm3(x)
+        x = x + self.cross_attn(xn, context, None, crossattn_cache=crossattn_cache)
         y = self.ffn(norm_modulate(self.norm2, x, scale_f, shift_f))
         return add_gated(x, y, gate_f)
 
@@ -306,6 +312,13 @@ class CausalWanModel(nn.Module):
         starts = CA.HostStarts(current_start, CA.host_starts(current_start, bsz)) \
             if isinstance(current_start, torch.Tensor) else current_start
 
+        # modulation + timestep embedding of every block of this range in one launch (the same element-wise
+        # sums the blocks would form one by one)
+        first_block, end_block = lo // 2, (hi + 1) // 2
+        mods = None
+        if end_block - first_block > 1:
+            mods = self._stacked_modulation(first_block, end_block) + e0.unsqueeze(0)
+
         stamps = self.half_stamps
         h = lo
         while h < hi:
@@ -318,10 +331,8 @@ class CausalWanModel(nn.Module):
                 part, step = "attn", 1
             t0 = _stamp(x) if stamps is not None else None
             block = self.blocks[idx]
-            if part == "all":
-                x = block(x, e0, grid_sizes, self.freqs, ctx, kv_cache[idx], crossattn_cache[idx], starts)
-            else:
-                x = block(x, e0, grid_sizes, self.freqs, ctx, kv_cache[idx], crossattn_cache[idx], starts, part=part)
+            x = block(x, e0, grid_sizes, self.freqs, ctx, kv_cache[idx], crossattn_cache[idx], starts, part=part,
+                      modulated=None if mods is None else mods[idx - first_block])
             if stamps is not None:
                 stamps.append((h, t0, _stamp(x)))
             h += step
@@ -330,6 +341,18 @@ class CausalWanModel(nn.Module):
 
         x = self.head(x, e.unflatten(0, t.shape).unsqueeze(2))
         return self.unpatchify(x, (frames, gh, gw))
+
+    def _stacked_modulation(self, first: int, end: int) -> torch.Tensor:
+        """[end - first, 1, 1, 6, C]: the blocks' modulation parameters side by side, rebuilt when one of
+        them was written or replaced."""
+        params = [self.blocks[i].modulation for i in range(first, end)]
+        key = (first, end) + tuple((p.data_ptr(), p._version) for p in params)
+        cached = getattr(self, "_mod_stack", None)
+        if cached is None or cached[0] != key:
+            with torch.no_grad():
+                cached = (key, torch.stack([p.detach() for p in params]).unsqueeze(1))
+            self._mod_stack = cached
+        return cached[1]
 
     def unpatchify(self, x, grid):
         """[B, F, gh*gw, p0*p1*p2*C] -> [B, C, F*p0, gh*p1, gw*p2]."""

@@ -310,6 +310,19 @@ def test_fused_block_elementwise_match_their_op_chains():
     got = ops.gate_residual(x, y, gate, F)
     assert torch.equal(got, want)
 
+    # norm3: LayerNorm with weight and bias, at the 1.3B and the 14B row length
+    for d in (dim, 5120, 264):
+        xd = (torch.randn(3, 777, d, generator=g) * 3 + 0.5).to(torch.bfloat16).cuda()
+        norm = torch.nn.LayerNorm(d, eps=1e-6).cuda().to(torch.bfloat16)
+        with torch.no_grad():
+            norm.weight.copy_(1 + 0.2 * torch.randn(d, generator=g))
+            norm.bias.copy_(0.3 * torch.randn(d, generator=g))
+            assert ops.can_fuse_layernorm(xd, norm)
+            # where weight * normalised and bias cancel, the step is that of the bias, not of the small sum
+            close(ops.layernorm_affine(xd, norm.weight, norm.bias, norm.eps), norm(xd), f'layernorm_affine {d}',
+                  scale_ref=norm.bias.expand_as(xd))
+    assert not ops.can_fuse_layernorm(xd.float(), norm)
+
 
 def test_block_forward_with_reference_arguments_equals_the_block_it_replaces():
     """`install()` binds `block_forward` (the reference block's argument list) onto reference blocks.
