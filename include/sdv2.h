@@ -281,6 +281,13 @@ int sdv2_attn_kvcache_static(const sdv2_view* q, const sdv2_view* k_cache, const
  *   with elementwise_affine on bf16 tensors, the block's norm3 in front of the text cross-attention
  *   (models/wan/causal_model.py:473-476; WanLayerNorm, models/wan/wan_base/modules/model.py:89-100);
  *   x, out contiguous [n_rows, dim], dim at most 5120.
+ * sdv2_residual_layernorm: x_out = bf16(x + bf16(y * gate[b,f])) (gate null: bf16(x + y)), then out = the
+ *   modulated LayerNorm (affine = 0: mul / add are scale / shift addressed like sdv2_ln_modulate's) or the affine
+ *   LayerNorm (affine = 1: mul / add are weight / bias) of x_out, in one pass over the rows: the residual
+ *   addition after self-attention together with norm3 (models/wan/causal_model.py:470-476), and the one
+ *   after the text cross-attention together with norm2 and its modulation (:473-480).  Bit for bit the
+ *   result of sdv2_gate_residual (or a bf16 addition) followed by sdv2_layernorm_affine / sdv2_ln_modulate.
+ *   x_out may alias x; dim at most 5120.
  * dim must be a multiple of 8 and at most 8192; all pointers 16-byte aligned.
  */
 int sdv2_rmsnorm(const void* x, int64_t x_row_stride, const void* weight, void* out, int64_t out_row_stride,
@@ -291,6 +298,9 @@ int sdv2_gate_residual(const void* x, const void* y, const void* gate, int64_t m
                        int frames, int tokens_per_frame, int dim, void* stream);
 int sdv2_layernorm_affine(const void* x, const void* weight, const void* bias, void* out, int64_t n_rows, int dim,
                           float eps, void* stream);
+int sdv2_residual_layernorm(const void* x, const void* y, const void* gate, int64_t gate_row_stride, void* x_out,
+                            int affine, const void* mul, const void* add, int64_t mod_row_stride, void* out,
+                            int batch, int frames, int tokens_per_frame, int dim, float eps, void* stream);
 
 /* Synchronises `stream`, reads the status word at the start of a workspace and clears it.
  * Returns SDV2_OK, SDV2_ERR_TIMEOUT (a device-side wait ran out; *detail = where),

@@ -304,11 +304,20 @@ def block_forward(self, x, e, seq_lens, grid_sizes, freqs, context, context_lens
 
     y = self.self_attn(norm_modulate(self.norm1, x, scale_a, shift_a), seq_lens, grid_sizes, freqs, block_mask,
                        kv_cache, current_start, current_end, causal_rope_cache)
-    x = add_gated(x, y, gate_a)
-    xn = ops.layernorm_affine(x, self.norm3.weight, self.norm3.bias, self.norm3.eps) \
-        if fused and ops.can_fuse_layernorm(x, self.norm3) else self.norm3(x)
-    x = x + self.cross_attn(xn, context, context_lens, crossattn_cache=crossattn_cache)
-    y = self.ffn(norm_modulate(self.norm2, x, scale_f, shift_f))
+    # where a residual addition is followed by a LayerNorm of its result, both run as one launch
+    if fused and ops.can_fuse_layernorm(x, self.norm3):
+        x, xn = ops.residual_layernorm(x, y, gate_a, frames, self.norm3.eps, weight=self.norm3.weight,
+                                       bias=self.norm3.bias)
+    else:
+        x = add_gated(x, y, gate_a)
+        xn = self.norm3(x)
+    c = self.cross_attn(xn, context, context_lens, crossattn_cache=crossattn_cache)
+    if fused and getattr(self.norm2, "weight", None) is None and x.shape[-1] <= 5120:
+        x, h = ops.residual_layernorm(x, c, None, frames, self.norm2.eps, scale=scale_f, shift=shift_f)
+    else:
+        x = x + c
+        h = norm_modulate(self.norm2, x, scale_f, shift_f)
+    y = self.ffn(h)
     return add_gated(x, y, gate_f)
 
 

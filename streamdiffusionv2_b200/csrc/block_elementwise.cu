@@ -7,6 +7,7 @@
 //   ln_modulate    : bf16( bf16( bf16(LN(x)) * bf16(1 + scale[b, frame]) ) + shift[b, frame] )  per token row
 //   gate_residual  : bf16( x + bf16(y * gate[b, frame]) )                              per element
 //   layernorm_affine: bf16( w * ((x - mean) * rstd) + b )                             per token row
+//   residual_layernorm: x_new = gate_residual(x, y, gate) or bf16(x + y), then either LayerNorm form of x_new
 //
 // All of them are pure streaming kernels (one read and one write of [tokens, dim], plus y for the
 // last), bound by HBM bandwidth; 16-byte vector accesses, one token row per block for the two
@@ -52,6 +53,11 @@ struct RowParams {
   const __nv_bfloat16* shift;    // ln_modulate: shift, same addressing
   int64_t mod_stride;
   int tokens_per_batch, tokens_per_frame, frames;
+  // ln_rows_kernel with a residual in front: x_new = bf16(x + y) or bf16(x + bf16(y * gate[b, frame]))
+  const __nv_bfloat16* res_y;
+  const __nv_bfloat16* res_gate;  // row (b * frames + f) at gate_stride elements; null = plain addition
+  __nv_bfloat16* res_out;         // x_new, rows of dim elements
+  int64_t gate_stride;
 };
 
 template <bool kLayerNorm>
@@ -158,7 +164,10 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-template <int kVecPerLane, bool kAffine>
+// kResidual: the row normalised is x_new = x + y (optionally y * gate first, rounded as the separate
+// gate_residual kernel rounds it), and x_new is written out as well: the block's residual additions in
+// front of norm3 and norm2 cost no launch and no second pass over the row.
+template <int kVecPerLane, bool kAffine, bool kResidual>
 __global__ void __launch_bounds__(kLnWarps * 32) ln_rows_kernel(const __grid_constant__ RowParams p) {
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + (threadIdx.x >> 5);
@@ -170,6 +179,37 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_rows_kernel(const __grid_con
   for (int i = 0; i < kVecPerLane; ++i) {
     const int c = lane + i * 32;
     v[i] = c < n_vec ? xr[c] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  const int64_t batch = row / p.tokens_per_batch;   // (unused by the affine form without a residual)
+  const int frame = static_cast<int>((row - batch * p.tokens_per_batch) / p.tokens_per_frame);
+  if (kResidual) {
+    const uint4* yr = reinterpret_cast<const uint4*>(p.res_y + row * static_cast<int64_t>(p.dim));
+    const uint4* gr = p.res_gate == nullptr ? nullptr
+        : reinterpret_cast<const uint4*>(p.res_gate + (batch * p.frames + frame) * p.gate_stride);
+    uint4* xo = reinterpret_cast<uint4*>(p.res_out + row * static_cast<int64_t>(p.dim));
+#pragma unroll
+    for (int i = 0; i < kVecPerLane; ++i) {
+      const int c = lane + i * 32;
+      if (c < n_vec) {
+        const uint4 yv = yr[c];
+        const uint32_t xw[4] = {v[i].x, v[i].y, v[i].z, v[i].w}, yw[4] = {yv.x, yv.y, yv.z, yv.w};
+        uint32_t gw[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};
+        if (gr != nullptr) {
+          const uint4 gv = __ldg(gr + c);
+          gw[0] = gv.x; gw[1] = gv.y; gw[2] = gv.z; gw[3] = gv.w;
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // without a gate y is added as it is (bf16(y * 1) == y)
+          const float lo = lo_f(xw[j]) + (gr != nullptr ? bf16_round(lo_f(yw[j]) * lo_f(gw[j])) : lo_f(yw[j]));
+          const float hi = hi_f(xw[j]) + (gr != nullptr ? bf16_round(hi_f(yw[j]) * hi_f(gw[j])) : hi_f(yw[j]));
+          o[j] = pack_bf16x2(lo, hi);
+        }
+        v[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        xo[c] = v[i];
+      }
+    }
   }
   float s = 0.f;
 #pragma unroll
@@ -198,9 +238,7 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_rows_kernel(const __grid_con
     mul = reinterpret_cast<const uint4*>(p.w);
     add = reinterpret_cast<const uint4*>(p.shift);
   } else {
-    const int64_t b = row / p.tokens_per_batch;
-    const int f = static_cast<int>((row - b * p.tokens_per_batch) / p.tokens_per_frame);
-    const int64_t off = (b * p.frames + f) * p.mod_stride;
+    const int64_t off = (batch * p.frames + frame) * p.mod_stride;
     mul = reinterpret_cast<const uint4*>(p.scale1p + off);
     add = reinterpret_cast<const uint4*>(p.shift + off);
   }
@@ -231,16 +269,16 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_rows_kernel(const __grid_con
 }
 
 // Picks the instantiation whose lanes hold the whole row; false when the row is longer than any of them.
-template <bool kAffine>
+template <bool kAffine, bool kResidual>
 bool launch_ln_rows(const RowParams& p, cudaStream_t stream) {
   const int per_lane = ((p.dim >> 3) + 31) / 32;
   const unsigned grid = static_cast<unsigned>((p.n_rows + kLnWarps - 1) / kLnWarps);
   if (per_lane <= 6)
-    ln_rows_kernel<6, kAffine><<<grid, kLnWarps * 32, 0, stream>>>(p);
+    ln_rows_kernel<6, kAffine, kResidual><<<grid, kLnWarps * 32, 0, stream>>>(p);
   else if (per_lane <= 8)
-    ln_rows_kernel<8, kAffine><<<grid, kLnWarps * 32, 0, stream>>>(p);
+    ln_rows_kernel<8, kAffine, kResidual><<<grid, kLnWarps * 32, 0, stream>>>(p);
   else if (per_lane <= 20)
-    ln_rows_kernel<20, kAffine><<<grid, kLnWarps * 32, 0, stream>>>(p);
+    ln_rows_kernel<20, kAffine, kResidual><<<grid, kLnWarps * 32, 0, stream>>>(p);
   else
     return false;
   return true;
@@ -329,7 +367,7 @@ extern "C" int sdv2_ln_modulate(const void* x, const void* scale1p, const void* 
   p.frames = frames;
   p.tokens_per_frame = tokens_per_frame;
   p.tokens_per_batch = frames * tokens_per_frame;
-  if (!sdv2::launch_ln_rows<false>(p, static_cast<cudaStream_t>(stream)))  // rows of more than 5120 elements
+  if (!sdv2::launch_ln_rows<false, false>(p, static_cast<cudaStream_t>(stream)))  // rows of more than 5120 elements
     sdv2::row_norm_kernel<true><<<static_cast<unsigned>(n_rows), sdv2::kRowThreads, 0,
                                   static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
@@ -349,7 +387,49 @@ extern "C" int sdv2_layernorm_affine(const void* x, const void* weight, const vo
   p.eps = eps;
   p.w = static_cast<const __nv_bfloat16*>(weight);
   p.shift = static_cast<const __nv_bfloat16*>(bias);
-  if (!sdv2::launch_ln_rows<true>(p, static_cast<cudaStream_t>(stream))) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  p.frames = 1;
+  p.tokens_per_frame = p.tokens_per_batch = static_cast<int>(n_rows);
+  if (!sdv2::launch_ln_rows<true, false>(p, static_cast<cudaStream_t>(stream))) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
+}
+
+extern "C" int sdv2_residual_layernorm(const void* x, const void* y, const void* gate, int64_t gate_row_stride,
+                                       void* x_out, int affine, const void* mul, const void* add,
+                                       int64_t mod_row_stride, void* out, int batch, int frames,
+                                       int tokens_per_frame, int dim, float eps, void* stream) {
+  if (!x || !y || !x_out || !mul || !add || !out || batch <= 0 || frames <= 0 || tokens_per_frame <= 0 || dim <= 0)
+    return SDV2_ERR_INVALID_ARG;
+  if (dim % 8 || dim > 5120) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  if (!a16(x) || !a16(y) || !a16(x_out) || !a16(mul) || !a16(add) || !a16(out) || (gate && !a16(gate)))
+    return SDV2_ERR_MISALIGNED;
+  if (gate && (gate_row_stride < dim || gate_row_stride % 8)) return SDV2_ERR_MISALIGNED;
+  if (!affine && (mod_row_stride < dim || mod_row_stride % 8)) return SDV2_ERR_MISALIGNED;
+  const int64_t n_rows = static_cast<int64_t>(batch) * frames * tokens_per_frame;
+  if (n_rows > 0x7FFFFFFFLL) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  sdv2::RowParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.x_stride = p.out_stride = dim;
+  p.n_rows = n_rows;
+  p.dim = dim;
+  p.eps = eps;
+  if (affine) {
+    p.w = static_cast<const __nv_bfloat16*>(mul);
+  } else {
+    p.scale1p = static_cast<const __nv_bfloat16*>(mul);
+    p.mod_stride = mod_row_stride;
+  }
+  p.shift = static_cast<const __nv_bfloat16*>(add);
+  p.frames = frames;
+  p.tokens_per_frame = tokens_per_frame;
+  p.tokens_per_batch = frames * tokens_per_frame;
+  p.res_y = static_cast<const __nv_bfloat16*>(y);
+  p.res_gate = static_cast<const __nv_bfloat16*>(gate);
+  p.res_out = static_cast<__nv_bfloat16*>(x_out);
+  p.gate_stride = gate_row_stride;
+  const bool ok = affine ? sdv2::launch_ln_rows<true, true>(p, static_cast<cudaStream_t>(stream))
+                         : sdv2::launch_ln_rows<false, true>(p, static_cast<cudaStream_t>(stream));
+  if (!ok) return SDV2_ERR_UNSUPPORTED_SHAPE;
   return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
 }
 

@@ -354,6 +354,33 @@ def layernorm_affine(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, 
     return out
 
 
+def residual_layernorm(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor], frames: int, eps: float, *,
+                       weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                       scale: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None):
+    """(x_new, normed): x_new = gate_residual(x, y, gate) (gate None: x + y), normed = layernorm_affine(x_new,
+    weight, bias) when weight / bias are given, else ln_modulate(x_new, scale, shift) - one launch, the same
+    values as the separate calls.  x [B, L, dim] with L a multiple of frames; dim at most 5120."""
+    B, L, dim = x.shape
+    x, y = x.contiguous(), y.contiguous()
+    x_new, out = torch.empty_like(x), torch.empty_like(x)
+    gt, gstride = (None, 0) if gate is None else _mod_rows(gate, B, frames, dim)
+    affine = weight is not None
+    if affine:
+        mul, add, stride = weight, bias, 0
+    else:
+        mul, stride = _mod_rows(scale, B, frames, dim)
+        add, stride2 = _mod_rows(shift, B, frames, dim)
+        if stride2 != stride:
+            mul, add, stride = mul.contiguous(), add.contiguous(), dim
+    with _Logged("residual_layernorm", 4.0 * x.numel() * 2):
+        rc = N.lib().sdv2_residual_layernorm(x.data_ptr(), y.data_ptr(), None if gt is None else gt.data_ptr(), gstride,
+                                             x_new.data_ptr(), 1 if affine else 0, mul.data_ptr(), add.data_ptr(),
+                                             stride, out.data_ptr(), B, frames, L // frames, dim, eps,
+                                             N.stream_ptr(x.device))
+    N.check(rc, "sdv2_residual_layernorm")
+    return x_new, out
+
+
 def can_fuse_layernorm(x: torch.Tensor, norm) -> bool:
     """Whether `norm` (an affine LayerNorm over the last dimension) applied to `x` can run as
     `layernorm_affine`."""

@@ -23,6 +23,10 @@ from . import causal_attention as CA
 from . import ops
 
 
+# Residual addition + the LayerNorm of its result as one launch (ops.residual_layernorm); False runs them apart.
+FUSE_RESIDUAL_LN = True
+
+
 def _fusable(x: torch.Tensor) -> bool:
     """The fused element-wise kernels serve bf16 CUDA tensors; anything else (the fp32 CPU runs
     of the tests) takes the PyTorch op chain they reproduce."""
@@ -143,16 +147,30 @@ class DiTBlock(nn.Module):
                 return ops.gate_residual(x, y, gate, frames)
             return x + (y.unflatten(1, (frames, per_frame)) * gate).flatten(1, 2)
 
+        # where a residual addition is followed by a LayerNorm of its result, both run as one launch
+        fuse3 = fused and ops.can_fuse_layernorm(x, self.norm3)
+        fuse2 = fused and FUSE_RESIDUAL_LN and x.shape[-1] <= 5120
+        xn = None
         if part != "rest":
             y = self.self_attn(norm_modulate(self.norm1, x, scale_a, shift_a), None, grid_sizes, freqs, None,
                                kv_cache, current_start, None)
-            x = add_gated(x, y, gate_a)
+            if fuse3 and FUSE_RESIDUAL_LN and part == "all":
+                x, xn = ops.residual_layernorm(x, y, gate_a, frames, self.norm3.eps, weight=self.norm3.weight,
+                                               bias=self.norm3.bias)
+            else:
+                x = add_gated(x, y, gate_a)
             if part == "attn":
                 return x
-        xn = ops.layernorm_affine(x, self.norm3.weight, self.norm3.bias, self.norm3.eps) \
-            if fused and ops.can_fuse_layernorm(x, self.norm3) else self.norm3(x)
-        x = x + self.cross_attn(xn, context, None, crossattn_cache=crossattn_cache)
-        y = self.ffn(norm_modulate(self.norm2, x, scale_f, shift_f))
+        if xn is None:
+            xn = ops.layernorm_affine(x, self.norm3.weight, self.norm3.bias, self.norm3.eps) if fuse3 \
+                else self.norm3(x)
+        c = self.cross_attn(xn, context, None, crossattn_cache=crossattn_cache)
+        if fuse2:
+            x, h = ops.residual_layernorm(x, c, None, frames, self.norm2.eps, scale=scale_f, shift=shift_f)
+        else:
+            x = x + c
+            h = norm_modulate(self.norm2, x, scale_f, shift_f)
+        y = self.ffn(h)
         return add_gated(x, y, gate_f)
 
 

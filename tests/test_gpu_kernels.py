@@ -323,6 +323,19 @@ def test_fused_block_elementwise_match_their_op_chains():
                   scale_ref=norm.bias.expand_as(xd))
     assert not ops.can_fuse_layernorm(xd.float(), norm)
 
+    # a residual addition and the LayerNorm of its result in one launch: the values of the separate launches
+    norm = torch.nn.LayerNorm(dim, eps=1e-6).cuda().to(torch.bfloat16)
+    with torch.no_grad():
+        norm.weight.copy_(1 + 0.2 * torch.randn(dim, generator=g))
+        norm.bias.copy_(0.3 * torch.randn(dim, generator=g))
+        x_sep = ops.gate_residual(x, y, gate, F)
+        x_new, normed = ops.residual_layernorm(x, y, gate, F, 1e-6, weight=norm.weight, bias=norm.bias)
+        assert torch.equal(x_new, x_sep)
+        assert torch.equal(normed, ops.layernorm_affine(x_sep, norm.weight, norm.bias, 1e-6))
+        x_new, normed = ops.residual_layernorm(x, y, None, F, 1e-6, scale=scale, shift=shift)
+        assert torch.equal(x_new, x + y)
+        assert torch.equal(normed, ops.ln_modulate(x + y, scale, shift, F, 1e-6))
+
 
 def test_block_forward_with_reference_arguments_equals_the_block_it_replaces():
     """`install()` binds `block_forward` (the reference block's argument list) onto reference blocks.
