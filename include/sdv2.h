@@ -288,6 +288,12 @@ int sdv2_attn_kvcache_static(const sdv2_view* q, const sdv2_view* k_cache, const
  *   after the text cross-attention together with norm2 and its modulation (:473-480).  Bit for bit the
  *   result of sdv2_gate_residual (or a bf16 addition) followed by sdv2_layernorm_affine / sdv2_ln_modulate.
  *   x_out may alias x; dim at most 5120.
+ * sdv2_gelu_tanh: out = bf16(gelu(x)) with the tanh approximation (torch.nn.GELU(approximate="tanh"), the
+ *   activation between the block's two FFN projections, models/wan/causal_model.py:424-427), n bf16 elements
+ *   (a multiple of 8); out may alias x.  Evaluated as x * sigmoid(2u), which equals 0.5 x (1 + tanh(u)); for
+ *   x > -2.9 the rounded results are the op chain's (isolated single-step differences); below that the chain's
+ *   1 + tanh(u) cancels and its fp32 results are off by up to 3e-7, which is whole bf16 steps of values that
+ *   small, while this form stays within rounding of the exact function.
  * dim must be a multiple of 8 and at most 8192; all pointers 16-byte aligned.
  */
 int sdv2_rmsnorm(const void* x, int64_t x_row_stride, const void* weight, void* out, int64_t out_row_stride,
@@ -298,6 +304,7 @@ int sdv2_gate_residual(const void* x, const void* y, const void* gate, int64_t m
                        int frames, int tokens_per_frame, int dim, void* stream);
 int sdv2_layernorm_affine(const void* x, const void* weight, const void* bias, void* out, int64_t n_rows, int dim,
                           float eps, void* stream);
+int sdv2_gelu_tanh(const void* x, void* out, int64_t n, void* stream);
 int sdv2_residual_layernorm(const void* x, const void* y, const void* gate, int64_t gate_row_stride, void* x_out,
                             int affine, const void* mul, const void* add, int64_t mod_row_stride, void* out,
                             int batch, int frames, int tokens_per_frame, int dim, float eps, void* stream);

@@ -76,6 +76,7 @@ _SIGNATURES = {
     "sdv2_gate_residual": (C.c_int, [C.c_void_p] * 3 + [C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                                         C.c_void_p]),
     "sdv2_layernorm_affine": (C.c_int, [C.c_void_p] * 4 + [C.c_int64, C.c_int, C.c_float, C.c_void_p]),
+    "sdv2_gelu_tanh": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "sdv2_residual_layernorm": (C.c_int, [C.c_void_p] * 3 + [C.c_int64, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                                              C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                                              C.c_float, C.c_void_p]),

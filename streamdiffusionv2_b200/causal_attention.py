@@ -317,7 +317,7 @@ def block_forward(self, x, e, seq_lens, grid_sizes, freqs, context, context_lens
     else:
         x = x + c
         h = norm_modulate(self.norm2, x, scale_f, shift_f)
-    y = self.ffn(h)
+    y = ops.ffn(self.ffn, h) if fused else self.ffn(h)
     return add_gated(x, y, gate_f)
 
 

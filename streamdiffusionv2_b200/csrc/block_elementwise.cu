@@ -7,6 +7,7 @@
 //   ln_modulate    : bf16( bf16( bf16(LN(x)) * bf16(1 + scale[b, frame]) ) + shift[b, frame] )  per token row
 //   gate_residual  : bf16( x + bf16(y * gate[b, frame]) )                              per element
 //   layernorm_affine: bf16( w * ((x - mean) * rstd) + b )                             per token row
+//   gelu_tanh      : bf16( x / (1 + exp(-2 sqrt(2/pi) (x + 0.044715 x^3))) )                per element
 //   residual_layernorm: x_new = gate_residual(x, y, gate) or bf16(x + y), then either LayerNorm form of x_new
 //
 // All of them are pure streaming kernels (one read and one write of [tokens, dim], plus y for the
@@ -318,10 +319,46 @@ __global__ void __launch_bounds__(256) gate_residual_kernel(const __grid_constan
   }
 }
 
+// tanh-approximated GELU, 0.5 x (1 + tanh(u)) with u = sqrt(2/pi) (x + 0.044715 x^3), evaluated as
+// x / (1 + exp(-2u)): the same function without the cancellation in 1 + tanh(u), a handful of instructions
+// per element, so the kernel streams at memory speed (the libm tanh of the op chain is compute-bound).
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * (x * x * x));
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(u * -2.8853900817779268f));  // exp(-2u)
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  return x * r;
+}
+
+__global__ void __launch_bounds__(256) gelu_tanh_kernel(const uint4* __restrict__ x, uint4* __restrict__ out,
+                                                        int64_t n_vec) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 v = x[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = pack_bf16x2(gelu_tanh(lo_f(w[j])), gelu_tanh(hi_f(w[j])));
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace sdv2
 
 namespace {
 bool a16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+}
+
+extern "C" int sdv2_gelu_tanh(const void* x, void* out, int64_t n, void* stream) {
+  if (!x || !out || n <= 0) return SDV2_ERR_INVALID_ARG;
+  if (n % 8) return SDV2_ERR_UNSUPPORTED_SHAPE;
+  if (!a16(x) || !a16(out)) return SDV2_ERR_MISALIGNED;
+  const int64_t n_vec = n >> 3;
+  int64_t blocks = (n_vec + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  sdv2::gelu_tanh_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), static_cast<uint4*>(out), n_vec);
+  return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
 }
 
 extern "C" int sdv2_rmsnorm(const void* x, int64_t x_row_stride, const void* weight, void* out,

@@ -381,6 +381,27 @@ def residual_layernorm(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Te
     return x_new, out
 
 
+def gelu_tanh_(x: torch.Tensor) -> torch.Tensor:
+    """tanh-approximated GELU of a contiguous bf16 tensor, in place."""
+    with _Logged("gelu_tanh", 2.0 * x.numel() * 2):
+        rc = N.lib().sdv2_gelu_tanh(x.data_ptr(), x.data_ptr(), x.numel(), N.stream_ptr(x.device))
+    N.check(rc, "sdv2_gelu_tanh")
+    return x
+
+
+def ffn(seq, h: torch.Tensor) -> torch.Tensor:
+    """`seq(h)` for the block's FFN.  Linear -> GELU(tanh) -> Linear on a bf16 CUDA tensor runs the activation
+    with `gelu_tanh_` in place on the first projection's output; anything else runs the module as it is."""
+    if (h.is_cuda and h.dtype == torch.bfloat16 and isinstance(seq, torch.nn.Sequential) and len(seq) == 3
+            and isinstance(seq[1], torch.nn.GELU) and getattr(seq[1], "approximate", "none") == "tanh"
+            and isinstance(seq[0], torch.nn.Linear) and not torch.is_grad_enabled()):
+        u = seq[0](h)
+        if u.is_contiguous() and u.numel() % 8 == 0:
+            return seq[2](gelu_tanh_(u))
+        return seq[2](seq[1](u))
+    return seq(h)
+
+
 def can_fuse_layernorm(x: torch.Tensor, norm) -> bool:
     """Whether `norm` (an affine LayerNorm over the last dimension) applied to `x` can run as
     `layernorm_affine`."""

@@ -170,7 +170,7 @@ class DiTBlock(nn.Module):
         else:
             x = x + c
             h = norm_modulate(self.norm2, x, scale_f, shift_f)
-        y = self.ffn(h)
+        y = ops.ffn(self.ffn, h) if fused else self.ffn(h)
         return add_gated(x, y, gate_f)
 
 
