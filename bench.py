@@ -550,7 +550,9 @@ def run_single_gpu(args):
         torch.cuda.nvtx.range_push("timed")        # lets a profiler select the launches of the timed region
         regions = [timed(args.steps, resident_step)]
         ops.set_launch_log(None)
-        repeats = max(1, min(args.max_repeats, -(-int(args.min_seconds * 1e3) // max(int(regions[0]), 1))))
+        # at least three regions, so that the median survives one disturbed region
+        repeats = max(min(3, args.max_repeats),
+                      min(args.max_repeats, -(-int(args.min_seconds * 1e3) // max(int(regions[0]), 1))))
         for _ in range(repeats - 1):
             regions.append(timed(args.steps, resident_step))
         torch.cuda.nvtx.range_pop()
@@ -785,7 +787,9 @@ def run_pipeline(args):
         first_ms = max_over_ranks([region(resident)])[0]
         ops.set_launch_log(None)
         # repeat the region until the regions cover about two seconds (same count on every rank)
-        repeats = max(1, min(args.max_repeats, -(-int(args.min_seconds * 1e3) // max(int(first_ms), 1))))
+        # (at least three, so that the median survives one disturbed region)
+        repeats = max(min(3, args.max_repeats),
+                      min(args.max_repeats, -(-int(args.min_seconds * 1e3) // max(int(first_ms), 1))))
         regions = [first_ms] + max_over_ranks([region(resident) for _ in range(repeats - 1)])
         clocks = sampler.stop() if rank == 0 else None
         ms = statistics.median(regions)
@@ -907,7 +911,8 @@ def main():
     ap.add_argument("--reference-steps", type=int, default=6, help="timed chunk steps per reference GPU arm")
     ap.add_argument("--cpu-budget", type=float, default=90.0, help="--impl reference: seconds of CPU work")
     ap.add_argument("--min-seconds", type=float, default=2.0,
-                    help="the timed region of K steps is repeated until the regions cover this long; median counts")
+                    help="the timed region of K steps is repeated (at least three times) until the regions cover this long; "
+                         "median counts")
     ap.add_argument("--max-repeats", type=int, default=8)
     ap.add_argument("--no-graphs", dest="graphs", action="store_false",
                     help="launch every op of every step from Python instead of replaying steady steps from a CUDA graph")
