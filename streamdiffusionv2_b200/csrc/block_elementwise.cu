@@ -269,6 +269,40 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_rows_kernel(const __grid_con
   }
 }
 
+// RMS norm with one warp per token row, for rows of at most 2048 elements.  The sum of squares is formed in
+// exactly the order of row_norm_kernel (and therefore of the append kernel's fused norm): lane l holds the
+// vectors l + 32 g, g = 0..7, i.e. the partial sums the 256 threads of that kernel hold one each; group g is
+// reduced by the same butterfly as warp g there, and the eight group sums by the same tree.
+__global__ void __launch_bounds__(kLnWarps * 32) rms_rows_kernel(const __grid_constant__ RowParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + (threadIdx.x >> 5);
+  if (row >= p.n_rows) return;
+  const int n_vec = p.dim >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(p.x + row * p.x_stride);
+  uint4 v[8];
+  float g[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = lane + i * 32;
+    v[i] = c < n_vec ? xr[c] : make_uint4(0u, 0u, 0u, 0u);
+    g[i] = c < n_vec ? rms_accumulate(0.f, v[i]) : 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) g[i] = warp_sum(g[i]);
+  const float rstd = rms_rstd(rms_fold_groups(g), p.dim, p.eps);
+  const uint4* wv = reinterpret_cast<const uint4*>(p.w);
+  uint4* orow = reinterpret_cast<uint4*>(p.out + row * p.out_stride);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = lane + i * 32;
+    if (c < n_vec) {
+      const uint4 m = __ldg(wv + c);
+      orow[c] = make_uint4(rms_scale_pair(v[i].x, rstd, m.x), rms_scale_pair(v[i].y, rstd, m.y),
+                           rms_scale_pair(v[i].z, rstd, m.z), rms_scale_pair(v[i].w, rstd, m.w));
+    }
+  }
+}
+
 // Picks the instantiation whose lanes hold the whole row; false when the row is longer than any of them.
 template <bool kAffine, bool kResidual>
 bool launch_ln_rows(const RowParams& p, cudaStream_t stream) {
@@ -376,8 +410,12 @@ extern "C" int sdv2_rmsnorm(const void* x, int64_t x_row_stride, const void* wei
   p.dim = dim;
   p.eps = eps;
   p.w = static_cast<const __nv_bfloat16*>(weight);
-  sdv2::row_norm_kernel<false><<<static_cast<unsigned>(n_rows), sdv2::kRowThreads, 0,
-                                 static_cast<cudaStream_t>(stream)>>>(p);
+  if (dim <= 2048)
+    sdv2::rms_rows_kernel<<<static_cast<unsigned>((n_rows + sdv2::kLnWarps - 1) / sdv2::kLnWarps), sdv2::kLnWarps * 32,
+                            0, static_cast<cudaStream_t>(stream)>>>(p);
+  else
+    sdv2::row_norm_kernel<false><<<static_cast<unsigned>(n_rows), sdv2::kRowThreads, 0,
+                                   static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? SDV2_OK : SDV2_ERR_CUDA;
 }
 
