@@ -396,7 +396,7 @@ def ffn(seq, h: torch.Tensor) -> torch.Tensor:
             and isinstance(seq[1], torch.nn.GELU) and getattr(seq[1], "approximate", "none") == "tanh"
             and isinstance(seq[0], torch.nn.Linear) and not torch.is_grad_enabled()):
         u = seq[0](h)
-        if u.is_contiguous() and u.numel() % 8 == 0:
+        if u.dtype == torch.bfloat16 and u.is_contiguous() and u.numel() % 8 == 0:
             return seq[2](gelu_tanh_(u))
         return seq[2](seq[1](u))
     return seq(h)
