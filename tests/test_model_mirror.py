@@ -175,3 +175,29 @@ def test_concatenated_qkv_weight_follows_the_parameters():
     attn.q.weight = torch.nn.Parameter(torch.zeros(256, 256))                 # replaced outright
     assert float(_fused_qkv_weights(attn)[0][:256].abs().max()) == 0.0
     assert sorted(n for n, _ in attn.named_parameters()) == names            # nothing was registered on the module
+
+
+def test_stacked_modulation_follows_the_parameters():
+    """The blocks' `modulation + e` sums are formed in one launch from a stacked copy of the blocks' modulation
+    parameters; the copy is rebuilt when a parameter is written or replaced, covers exactly the block range
+    asked for, and registers nothing on the model."""
+    from streamdiffusionv2_b200.wan_model import CausalWanModel
+    torch.manual_seed(0)
+    m = CausalWanModel(**cases.MODEL_KW)
+    names = sorted(n for n, _ in m.named_parameters())
+    n = len(m.blocks)
+    s = m._stacked_modulation(0, n)
+    assert s.shape == (n, 1, 1, 6, m.dim)
+    assert all(torch.equal(s[i, 0], m.blocks[i].modulation) for i in range(n))
+    assert m._stacked_modulation(0, n) is s                                   # cached while nothing changes
+    with torch.no_grad():
+        m.blocks[1].modulation.add_(1.0)                                      # in place: the version counter moves
+    s2 = m._stacked_modulation(0, n)
+    assert s2 is not s and torch.equal(s2[1, 0], m.blocks[1].modulation)
+    m.blocks[0].modulation = torch.nn.Parameter(torch.zeros_like(m.blocks[0].modulation))   # replaced outright
+    assert float(m._stacked_modulation(0, n)[0].abs().max()) == 0.0
+    part = m._stacked_modulation(1, n)                                        # a stage's own range
+    assert part.shape[0] == n - 1 and torch.equal(part[0, 0], m.blocks[1].modulation)
+    e = torch.randn(2, 3, 6, m.dim)
+    assert torch.equal((part + e.unsqueeze(0))[0], m.blocks[1].modulation.unsqueeze(1) + e)
+    assert sorted(k for k, _ in m.named_parameters()) == names
