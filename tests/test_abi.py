@@ -48,6 +48,18 @@ def test_argument_validation_without_a_gpu(built_lib):
     assert lib.sdv2_attn_kvcache(*args(v), 1, 4, 1, 128, 4, lens, 0.1, None, 0, None) == -6    # workspace
     assert lib.sdv2_attn_kvcache(*args(v), 1, 4, 1, 128, 3, lens, 0.1, ws, 256, None) == -1    # len > cache
     assert lib.sdv2_attn_kvcache(*args(v), 65, 4, 1, 128, 4, lens, 0.1, ws, 256, None) == -2   # rows
+    # the element-wise entry points
+    a, odd = 0x1000, 0x1008
+    assert lib.sdv2_gelu_tanh(None, a, 64, None) == -1                                          # null input
+    assert lib.sdv2_gelu_tanh(a, a, 12, None) == -2                                             # not whole vectors
+    assert lib.sdv2_gelu_tanh(odd, a, 64, None) == -3                                           # alignment
+    assert lib.sdv2_layernorm_affine(a, a, a, a, 4, 5128, 1e-6, None) == -2                     # row too long
+    assert lib.sdv2_layernorm_affine(a, a, None, a, 4, 1536, 1e-6, None) == -1                  # no bias
+    assert lib.sdv2_layernorm_affine(a, odd, a, a, 4, 1536, 1e-6, None) == -3
+    assert lib.sdv2_residual_layernorm(a, None, None, 0, a, 1, a, a, 0, a, 1, 1, 4, 1536, 1e-6, None) == -1   # no y
+    assert lib.sdv2_residual_layernorm(a, a, a, 1000, a, 1, a, a, 0, a, 1, 1, 4, 1536, 1e-6, None) == -3      # gate rows overlap
+    assert lib.sdv2_residual_layernorm(a, a, None, 0, a, 0, a, a, 1000, a, 1, 1, 4, 1536, 1e-6, None) == -3   # modulation rows overlap
+    assert lib.sdv2_residual_layernorm(a, a, None, 0, a, 0, a, a, 9216, a, 1, 1, 4, 5128, 1e-6, None) == -2   # row too long
 
 
 def test_no_fallback_when_library_missing(monkeypatch, tmp_path):
